@@ -1,0 +1,287 @@
+"""GPU parity: the sm_100a kernels, called through the C ABI, against the CPU oracle and against the
+fixtures produced by the reference code.  Every test needs a B200."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from make_golden import case_inputs
+from oracle import xattn_oracle as orc
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+DEV = "cuda"
+
+
+def _load(name):
+    z = np.load(os.path.join(GOLD, name))
+    return z, json.loads(str(z["specs"]))
+
+
+def _thr(spec):
+    t = spec["threshold"]
+    return torch.tensor(t, dtype=torch.float32) if isinstance(t, list) else t
+
+
+def _unpack_mask(z, i, shape):
+    return torch.from_numpy(np.unpackbits(z[f"mask_{i}"])[: int(np.prod(shape))].reshape(shape).astype(bool))
+
+
+@pytest.fixture(autouse=True)
+def _status_clean():
+    import xattn_b200
+    yield
+    xattn_b200.check_device_status()
+
+
+def _assert_masks(mask, ref_mask, ref_sums, spec):
+    exempt = orc.margin_exempt(ref_sums, spec["q_len"], spec["k_len"], 128, spec["stride"], spec["chunk"],
+                               _thr(spec), spec["causal"])
+    diff = (mask != ref_mask) & ~exempt
+    assert not diff.any(), f"{int(diff.sum())} non-exempt mask mismatches at {diff.nonzero()[:6].tolist()}"
+    # exemptions must stay the exception
+    assert int((mask != ref_mask).sum()) <= max(2, int(0.01 * mask.numel()))
+
+
+# sums tolerance: block sums are O(1) sums of fp32 softmax probabilities; the tensor-core product of
+# the (bf16 or split-fp32) inputs differs from the CPU fp32 product by ~1e-6 relative per score.
+SUMS_RTOL, SUMS_ATOL = 2e-4, 2e-5
+
+_zt, _st = _load("estimate_torch_path.npz")
+
+
+@pytest.mark.parametrize("i", range(len(_st)))
+def test_estimate_and_masks_vs_reference_fixtures(i):
+    """fp32 inputs (split-precision GEMM) and bf16 inputs against the reference's torch branch."""
+    import xattn_b200
+    spec = _st[i]
+    q, k = case_inputs(spec)
+    xattn_b200.set_estimate_semantics("torch")
+    sums, mask = xattn_b200.xattn_estimate(
+        q.to(DEV), k.to(DEV), 128, spec["stride"], threshold=_thr(spec), chunk_size=spec["chunk"],
+        causal=spec["causal"], keep_sink=spec["keep_sink"], keep_recent=spec["keep_recent"])
+    ref_sums = torch.from_numpy(_zt[f"sums_{i}"])
+    ref_mask = _unpack_mask(_zt, i, spec["mask_shape"])
+    assert sums.dtype == q.dtype and mask.dtype == torch.bool
+    assert tuple(mask.shape) == tuple(spec["mask_shape"])
+    tol = dict(rtol=SUMS_RTOL, atol=SUMS_ATOL) if q.dtype == torch.float32 else dict(rtol=1e-2, atol=1e-2)
+    assert torch.allclose(sums.float().cpu(), ref_sums, **tol), (sums.float().cpu() - ref_sums).abs().max()
+    _assert_masks(mask.cpu(), ref_mask, ref_sums, spec)
+
+
+def test_estimate_triton_semantics_vs_reference_fixtures():
+    import xattn_b200
+    z, specs = _load("estimate_triton_path.npz")
+    try:
+        xattn_b200.set_estimate_semantics("triton")
+        for i, spec in enumerate(specs):
+            q, k = case_inputs(spec)
+            sums, mask = xattn_b200.xattn_estimate(q.to(DEV), k.to(DEV), 128, spec["stride"], threshold=_thr(spec),
+                                                   chunk_size=spec["chunk"], causal=spec["causal"])
+            ref_sums = torch.from_numpy(z[f"sums_{i}"])
+            assert torch.allclose(sums.float().cpu(), ref_sums, rtol=SUMS_RTOL, atol=SUMS_ATOL)
+            _assert_masks(mask.cpu(), _unpack_mask(z, i, spec["mask_shape"]), ref_sums, spec)
+    finally:
+        xattn_b200.set_estimate_semantics("torch")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("hq,hkv", [(4, 4), (8, 2)])
+def test_estimate_16bit_inputs_vs_oracle(dtype, hq, hkv):
+    """bf16/fp16 inputs, GQA included: fp32 sums against the oracle run on the same rounded values."""
+    from xattn_b200 import ops, synth
+    gen = torch.Generator().manual_seed(11)
+    q, k, _ = synth.llama_like(gen, hq, hkv, 4096)
+    q, k = q.to(dtype), k.to(dtype)
+    for stride, chunk, causal, sem in ((16, 2048, True, "torch"), (8, 4096, True, "triton"), (8, 2048, False, "torch")):
+        got = ops.estimate_block_sums(q.to(DEV), k.to(DEV), stride, 128, chunk, 1.0, causal, semantics=sem).cpu()
+        want = orc.estimate_block_sums(q.float(), k.float().repeat_interleave(hq // hkv, 1), 128, stride, 1.0, chunk,
+                                       causal, sem)
+        assert torch.allclose(got, want, rtol=SUMS_RTOL, atol=SUMS_ATOL), (got - want).abs().max()
+
+
+def test_estimate_strided_layout_and_ragged_length():
+    """HF-style [B,L,H,D] storage viewed as [B,H,L,D], and a length that is not a multiple of the stride."""
+    from xattn_b200 import ops
+    g = torch.Generator().manual_seed(5)
+    L = 1003
+    q = torch.randn(1, L, 3, 128, generator=g).bfloat16().transpose(1, 2)
+    k = torch.randn(1, L, 3, 128, generator=g).bfloat16().transpose(1, 2)
+    got = ops.estimate_block_sums(q.to(DEV).transpose(1, 2).contiguous().transpose(1, 2),
+                                  k.to(DEV).transpose(1, 2).contiguous().transpose(1, 2), 16, 128, 2048, 1.0, True).cpu()
+    want = orc.estimate_block_sums(q.float(), k.float(), 128, 16, 1.0, 2048, True, "torch")
+    assert torch.allclose(got, want, rtol=SUMS_RTOL, atol=SUMS_ATOL), (got - want).abs().max()
+
+
+def test_select_vs_find_blocks_chunked_fixtures():
+    """The selection kernel alone, on the reference's own inputs/outputs: bit-exact outside the margin."""
+    import xattn_b200
+    z, specs = _load("find_blocks_chunked.npz")
+    for i, spec in enumerate(specs):
+        x = torch.from_numpy(z[f"x_{i}"])
+        ref = torch.from_numpy(z[f"mask_{i}"])
+        thr = _thr(spec)
+        got = xattn_b200.find_blocks_chunked(x.to(DEV), spec["current_index"], thr, None, decoding=False,
+                                             mode="prefill", causal=spec["causal"]).cpu()
+        ex = orc.margin_exempt_chunk(x, spec["current_index"], thr, spec["causal"])
+        d = (got != ref) & ~ex
+        assert not d.any(), (i, spec, d.nonzero()[:5].tolist())
+
+
+def test_select_lists_match_mask():
+    from xattn_b200 import ops
+    g = torch.Generator().manual_seed(9)
+    x = (torch.rand(1, 4, 32, 32, generator=g) ** 6) * torch.tril(torch.ones(32, 32))
+    mask, idx, cnt = ops.select_blocks(x.to(DEV), 16, 0, 0.9, True, True, list_shape=(4096 - 50, 4096 - 50))
+    mask, idx, cnt = mask.cpu(), idx.cpu(), cnt.cpu()
+    for h in range(4):
+        for r in range(32):
+            want = mask[0, h, r].nonzero().flatten().tolist()
+            assert idx[0, h, r, : cnt[0, h, r]].tolist() == want
+    idx2, cnt2 = ops.mask_to_lists(mask.to(DEV), 4096 - 50, 4096 - 50, True)
+    assert torch.equal(cnt2.cpu(), cnt)
+    for h in range(4):
+        for r in range(32):
+            assert torch.equal(idx2.cpu()[0, h, r, : cnt[0, h, r]], idx[0, h, r, : cnt[0, h, r]])
+
+
+def _random_block_mask(g, H, qb, kb, causal, density=0.35):
+    m = torch.rand(1, H, qb, kb, generator=g) < density
+    off = kb - qb
+    for r in range(qb):
+        m[:, :, r, min(off + r, kb - 1)] = True
+        m[:, :, r, 0] = True
+    if causal:
+        m &= torch.tril(torch.ones(qb, kb, dtype=torch.bool), diagonal=off)
+    return m
+
+
+# output tolerance of the attention phase: bf16 against the fp32 oracle under the same mask
+OUT_MAX_ABS, OUT_MEAN_ABS = 2e-2, 2e-3
+
+
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("hq,hkv,lq,lk", [(2, 2, 1024, 1024), (4, 1, 1000, 1000), (2, 2, 512, 1536), (2, 1, 300, 1100)])
+def test_block_sparse_attention_vs_oracle(causal, dtype, hq, hkv, lq, lk):
+    from xattn_b200 import ops
+    g = torch.Generator().manual_seed(lq + lk + hq)
+    q = torch.randn(1, hq, lq, 128, generator=g).to(dtype)
+    k = torch.randn(1, hkv, lk, 128, generator=g).to(dtype)
+    v = torch.randn(1, hkv, lk, 128, generator=g).to(dtype)
+    qb, kb = (lq + 127) // 128, (lk + 127) // 128
+    mask = _random_block_mask(g, hq, qb, kb, causal)
+    idx, cnt = ops.mask_to_lists(mask.to(DEV), lq, lk, causal)
+    out = ops.block_sparse_attention(q.to(DEV), k.to(DEV), v.to(DEV), idx, cnt, causal).float().cpu()
+    ref = orc.block_sparse_attention_oracle(q, k, v, mask, causal)
+    err = (out - ref).abs()
+    assert err.max() < OUT_MAX_ABS and err.mean() < OUT_MEAN_ABS, (err.max(), err.mean())
+
+
+def test_attention_rescale_path_and_empty_rows():
+    """Scores that grow block after block force the lazy rescale of O; rows with an empty list give zeros."""
+    from xattn_b200 import ops
+    g = torch.Generator().manual_seed(77)
+    L = 1024
+    q = torch.randn(1, 1, L, 128, generator=g)
+    k = torch.randn(1, 1, L, 128, generator=g)
+    k = k * torch.linspace(0.5, 6.0, L)[None, None, :, None]        # later keys dominate more and more
+    v = torch.randn(1, 1, L, 128, generator=g)
+    q, k, v = q.bfloat16(), k.bfloat16(), v.bfloat16()
+    mask = torch.tril(torch.ones(8, 8, dtype=torch.bool))[None, None].clone()
+    mask[0, 0, 3] = False                                            # an empty row
+    idx, cnt = ops.mask_to_lists(mask.to(DEV), L, L, True)
+    out = ops.block_sparse_attention(q.to(DEV), k.to(DEV), v.to(DEV), idx, cnt, True).float().cpu()
+    ref = orc.block_sparse_attention_oracle(q, k, v, mask, True)
+    assert torch.isfinite(out).all()
+    assert out[0, 0, 384:512].abs().max() == 0
+    err = (out - ref).abs()
+    assert err.max() < 3e-2 and err.mean() < OUT_MEAN_ABS, (err.max(), err.mean())
+
+
+def test_block_sparse_attn_func_mirror():
+    import xattn_b200
+    g = torch.Generator().manual_seed(1)
+    L, H = 640, 2
+    q = torch.randn(L, H, 128, generator=g).bfloat16()
+    k = torch.randn(L, H, 128, generator=g).bfloat16()
+    v = torch.randn(L, H, 128, generator=g).bfloat16()
+    mask = _random_block_mask(g, H, 5, 5, True)
+    cu = torch.tensor([0, L], dtype=torch.int32, device=DEV)
+    hm = torch.ones(H, dtype=torch.int32, device=DEV)
+    out = xattn_b200.block_sparse_attn_func(q.to(DEV), k.to(DEV), v.to(DEV), cu, cu, hm, None, mask.to(DEV), L, L,
+                                            p_dropout=0.0, deterministic=True, is_causal=True)
+    ref = orc.block_sparse_attention_oracle(q.transpose(0, 1)[None], k.transpose(0, 1)[None],
+                                            v.transpose(0, 1)[None], mask, True)
+    err = (out.float().cpu().transpose(0, 1)[None] - ref).abs()
+    assert err.max() < OUT_MAX_ABS and err.mean() < OUT_MEAN_ABS
+
+
+@pytest.mark.parametrize("name,L,heads", [("llama3_8b_32k", 8192, 2), ("llama3_8b_128k", 4096, 1)])
+def test_prefill_end_to_end_vs_oracle(name, L, heads):
+    """Xattention_prefill on a cut-down Llama workload: mask parity with the oracle, then output parity with
+    the oracle's attention under the mask the GPU produced."""
+    import xattn_b200
+    from xattn_b200 import ops, synth
+    q, k, v, w = synth.make_inputs(name, seed=3, heads_limit=heads, seq_len=L)
+    chunk = w.chunk_size or orc.default_chunk_size(L)
+    chunk = min(chunk, 2048) if L <= 4096 else chunk
+    rep = q.shape[1] // k.shape[1]
+    sums, mask = xattn_b200.xattn_estimate(q.to(DEV), k.to(DEV), 128, w.stride, threshold=w.threshold,
+                                           chunk_size=chunk, causal=True)
+    osums, omask = orc.xattn_estimate_oracle(q.float(), k.float().repeat_interleave(rep, 1), 128, w.stride, 1.0,
+                                             w.threshold, chunk, True)
+    ex = orc.margin_exempt(osums, L, L, 128, w.stride, chunk, w.threshold, True)
+    d = (mask.cpu() != omask) & ~ex
+    assert not d.any(), d.nonzero()[:6].tolist()
+    out = xattn_b200.Xattention_prefill(q.to(DEV), k.to(DEV), v.to(DEV), w.stride, threshold=w.threshold,
+                                        chunk_size=chunk, causal=True)
+    assert out.shape == q.shape and out.dtype == q.dtype
+    ref = orc.block_sparse_attention_oracle(q, k, v, mask.cpu()[:, :, : L // 128, : L // 128], True)
+    err = (out.float().cpu() - ref).abs()
+    assert err.max() < OUT_MAX_ABS and err.mean() < OUT_MEAN_ABS, (err.max(), err.mean())
+
+
+def test_prefill_dense_threshold_one_matches_sdpa():
+    """threshold=1 keeps every causal block with mass: the op must equal dense causal attention
+    (size-independent property, no oracle involved)."""
+    import xattn_b200
+    g = torch.Generator().manual_seed(2)
+    L = 2048
+    q = torch.randn(1, 2, L, 128, generator=g).bfloat16().to(DEV)
+    k = torch.randn(1, 2, L, 128, generator=g).bfloat16().to(DEV)
+    v = torch.randn(1, 2, L, 128, generator=g).bfloat16().to(DEV)
+    xattn_b200.set_estimate_semantics("triton")      # every past block carries mass under these semantics
+    try:
+        out = xattn_b200.Xattention_prefill(q, k, v, 8, threshold=1.0, chunk_size=2048, causal=True)
+    finally:
+        xattn_b200.set_estimate_semantics("torch")
+    ref = torch.nn.functional.scaled_dot_product_attention(q.float(), k.float(), v.float(), is_causal=True)
+    err = (out.float() - ref).abs()
+    assert err.max() < OUT_MAX_ABS and err.mean() < OUT_MEAN_ABS, (err.max(), err.mean())
+
+
+def test_runs_are_bit_identical():
+    """Same inputs, two runs: identical bits (no race between the roles of a CTA)."""
+    import xattn_b200
+    from xattn_b200 import synth
+    q, k, v, w = synth.make_inputs("llama3_8b_32k", seed=8, heads_limit=1, seq_len=4096)
+    a = xattn_b200.Xattention_prefill(q.to(DEV), k.to(DEV), v.to(DEV), 8, threshold=0.9, chunk_size=2048)
+    b = xattn_b200.Xattention_prefill(q.to(DEV), k.to(DEV), v.to(DEV), 8, threshold=0.9, chunk_size=2048)
+    assert torch.equal(a, b)
+
+
+def test_bad_arguments_raise_before_launch():
+    import xattn_b200
+    from xattn_b200._lib import XattnB200Error
+    q = torch.zeros(1, 2, 256, 128, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(ValueError):
+        xattn_b200.xattn_estimate(q, q, 128, 16, kdb=2)
+    with pytest.raises(NotImplementedError):
+        xattn_b200.xattn_estimate(q, q, 128, 16, select_mode="slash")
+    with pytest.raises((XattnB200Error, ValueError)):
+        xattn_b200.xattn_estimate(q, q, 128, 3)
+    with pytest.raises(AssertionError):
+        xattn_b200.Xattention_prefill(torch.cat([q, q]), torch.cat([q, q]), torch.cat([q, q]), 16)

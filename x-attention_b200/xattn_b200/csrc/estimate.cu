@@ -1,0 +1,507 @@
+// Phase 1 of the XAttention prefill path: antidiagonal block-importance estimate.
+//
+//   S'[i,j] = scale * sum_{t<S} Q[S*i + S-1-t, :] . K[S*j + t, :]        (one row/col = S tokens)
+//   P = row softmax of S' over the row's visible columns
+//   attn_sums[qb,kb] = sum of P over the (block/S) x (block/S) cell
+//
+// Reference: xattn/src/Xattention.py:71-136,174-252 (torch branch) and xattn/src/kernels.py:5-156,
+// 197-235 (Triton kernels).  Here the S' matrix never exists in memory:
+//
+//   est_setup_kernel     per 128-row tile, the range of 256-column tiles that hold visible columns
+//   est_gemm_kernel      persistent, warp-specialised tcgen05 GEMM.  One thread streams the
+//                        stride-reshaped operands with TMA (the reshape is a 5-D tensor map: a row of
+//                        the A tile for K-step t is token S*i+S-1-t, of the B tile token S*j+t), one
+//                        thread issues 128x256x16 MMAs into a double-buffered TMEM accumulator, four
+//                        warps run the epilogue: per row, max over the tile's visible columns, exp2,
+//                        sums over groups of block/S columns.  Output per (row, key block): an
+//                        un-normalised partial sum, plus the max it was taken against per (row, tile).
+//   est_finalize_kernel  per query block: combine the tiles' maxima, normalise and add the block/S rows.
+#include <math.h>
+
+#include "host_common.cuh"
+#include "sm100_primitives.cuh"
+
+namespace xb {
+
+constexpr int kTileM = 128;
+constexpr int kTileN = 256;
+constexpr int kTileK = 64;                                   // elements per TMA box row = 128 bytes
+constexpr int kStages = 4;
+constexpr int kABytes = kTileM * kTileK * 2;                 // 16 KiB
+constexpr int kBBytes = kTileN * kTileK * 2;                 // 32 KiB
+constexpr int kStageBytes = kABytes + kBBytes;               // 48 KiB
+constexpr int kGemmThreads = 192;                            // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue
+constexpr int kGemmSmem = kStages * kStageBytes + 1024 /*barriers*/ + 1024 /*alignment slack*/;
+
+struct EstGeom {
+  int batch, hq, hkv;
+  int S, d_chunks;             // K loop: S * d_chunks steps of 64 elements
+  int rows_total, cols_total;  // padded lengths / S
+  int rows_valid, cols_valid;  // rows past rows_valid give zeros; causal: columns past cols_valid are hidden
+  int rcs;                     // chunk_size / S
+  int row_off;                 // (k_chunks - q_chunks) * rcs: global position of row 0
+  int causal, left_blank;      // left_blank: columns left of the row's chunk are hidden (torch branch, un-padded K)
+  int rbs, kb_total, qb_total;
+  int n_mtiles, n_ntiles;
+  float scale_log2;
+};
+
+// Visible columns [lo, hi] of reshaped row i (empty when hi < lo).
+// causal, torch branch (Xattention.py:191-225): columns [chunk_start, chunk_start + i_local], minus the
+// K padding; when K is not padded the slice `[-0:]` at :201 hides everything left of the chunk too.
+// causal, Triton (kernels.py:56): columns <= global position of the row.  non-causal: everything.
+__host__ __device__ inline void row_bounds(const EstGeom& g, int i, int& lo, int& hi) {
+  if (i >= g.rows_valid) { lo = 1; hi = 0; return; }
+  if (!g.causal) { lo = 0; hi = g.cols_total - 1; return; }
+  const int chunk_start = (i / g.rcs) * g.rcs + g.row_off;
+  lo = g.left_blank ? chunk_start : 0;
+  hi = g.row_off + i;
+  if (hi > g.cols_valid - 1) hi = g.cols_valid - 1;
+}
+
+// tile_lo[mt], tile_prefix[mt] (exclusive prefix of tile counts, n_mtiles+1 entries)
+__global__ void est_setup_kernel(EstGeom g, int* __restrict__ tile_lo, int* __restrict__ tile_prefix) {
+  extern __shared__ int s_cnt[];
+  for (int mt = threadIdx.x; mt < g.n_mtiles; mt += blockDim.x) {
+    int lo_min = 0x7fffffff, hi_max = -1;
+    for (int r = 0; r < kTileM; ++r) {
+      const int i = mt * kTileM + r;
+      if (i >= g.rows_total) break;
+      int lo, hi;
+      row_bounds(g, i, lo, hi);
+      if (hi >= lo) {
+        lo_min = lo < lo_min ? lo : lo_min;
+        hi_max = hi > hi_max ? hi : hi_max;
+      }
+    }
+    if (hi_max < 0) {
+      tile_lo[mt] = 0;
+      s_cnt[mt] = 0;
+    } else {
+      tile_lo[mt] = lo_min / kTileN;
+      s_cnt[mt] = hi_max / kTileN - lo_min / kTileN + 1;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int mt = 0; mt < g.n_mtiles; ++mt) {
+      tile_prefix[mt] = acc;
+      acc += s_cnt[mt];
+    }
+    tile_prefix[g.n_mtiles] = acc;
+  }
+}
+
+__device__ __forceinline__ void decode_tile(const EstGeom& g, const int* __restrict__ tile_lo,
+                                            const int* __restrict__ tile_prefix, int tiles_per_head, int tile,
+                                            int& bh, int& mt, int& nt) {
+  bh = tile / tiles_per_head;
+  const int rem = tile - bh * tiles_per_head;
+  int lo = 0, hi = g.n_mtiles;   // find mt with prefix[mt] <= rem < prefix[mt+1]
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (__ldg(tile_prefix + mid) <= rem) lo = mid; else hi = mid;
+  }
+  mt = lo;
+  nt = __ldg(tile_lo + mt) + rem - __ldg(tile_prefix + mt);
+}
+
+template <int RBS>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+est_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const EstGeom g,
+                const int* __restrict__ tile_lo, const int* __restrict__ tile_prefix, float* __restrict__ partial,
+                float* __restrict__ mtile, const uint32_t idesc, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+  const uint32_t full0 = smem_u32(bars);                    // [kStages]
+  const uint32_t empty0 = smem_u32(bars + kStages);         // [kStages]
+  const uint32_t tfull0 = smem_u32(bars + 2 * kStages);     // [2]
+  const uint32_t tempty0 = smem_u32(bars + 2 * kStages + 2);// [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull0 + 8 * a, 1);
+      mbar_init(tempty0 + 8 * a, 4);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int tiles_per_head = __ldg(tile_prefix + g.n_mtiles);
+  const int total_tiles = tiles_per_head * g.batch * g.hq;
+  const int k_steps = g.S * g.d_chunks;
+  const int group = g.hq / g.hkv;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (one thread)
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
+        int bh, mt, nt;
+        decode_tile(g, tile_lo, tile_prefix, tiles_per_head, tile, bh, mt, nt);
+        const int b = bh / g.hq, h = bh - b * g.hq;
+        for (int ks = 0; ks < k_steps; ++ks, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          if (!mbar_wait(empty0 + 8 * s, ph ^ 1, abort_flag)) break;
+          const int t = ks / g.d_chunks;
+          const int dc = ks - t * g.d_chunks;
+          const uint32_t dstA = smem_u32(smem + s * kStageBytes);
+          mbar_expect_tx(full0 + 8 * s, kStageBytes);
+          tma_load_5d(dstA, &tmQ, full0 + 8 * s, dc * kTileK, g.S - 1 - t, mt * kTileM, h, b);
+          tma_load_5d(dstA + kABytes, &tmK, full0 + 8 * s, dc * kTileK, t, nt * kTileN, h / group, b);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (one thread)
+    if (lane == 0) {
+      uint32_t it = 0, local_tile = 0;
+      for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, ++local_tile) {
+        const uint32_t acc = local_tile & 1;
+        const uint32_t acc_ph = (local_tile >> 1) & 1;
+        if (!mbar_wait(tempty0 + 8 * acc, acc_ph ^ 1, abort_flag)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * kTileN;
+        bool ok = true;
+        for (int ks = 0; ks < k_steps; ++ks, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          if (!mbar_wait(full0 + 8 * s, ph, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + s * kStageBytes);
+          const uint32_t b_addr = a_addr + kABytes;
+#pragma unroll
+          for (int k4 = 0; k4 < kTileK / 16; ++k4) {
+            const uint64_t a_desc = smem_desc_sw128(a_addr + k4 * 32, 16, 1024);
+            const uint64_t b_desc = smem_desc_sw128(b_addr + k4 * 32, 16, 1024);
+            mma_ss(d_tmem, a_desc, b_desc, idesc, (ks > 0 || k4 > 0) ? 1u : 0u);
+          }
+          mma_commit(empty0 + 8 * s);          // stage reusable once these MMAs have read it
+        }
+        if (!ok) break;
+        mma_commit(tfull0 + 8 * acc);          // accumulator complete
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (4 warps, thread = tile row)
+    const int quad = warp & 3;                  // TMEM lane quarter this warp may access
+    const int r = quad * 32 + lane;
+    constexpr int kGroups = kTileN / RBS;       // key blocks per tile
+    uint32_t local_tile = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local_tile) {
+      int bh, mt, nt;
+      decode_tile(g, tile_lo, tile_prefix, tiles_per_head, tile, bh, mt, nt);
+      const uint32_t acc = local_tile & 1;
+      const uint32_t acc_ph = (local_tile >> 1) & 1;
+      const int i = mt * kTileM + r;
+      int lo, hi;
+      row_bounds(g, i, lo, hi);
+      const int n0 = nt * kTileN;
+      const int clo = lo - n0 > 0 ? lo - n0 : 0;
+      const int chi = hi - n0 < kTileN - 1 ? hi - n0 : kTileN - 1;
+      // warp-uniform: the tensor-memory loads below are warp-collective
+      if (!__all_sync(0xffffffffu, mbar_wait(tfull0 + 8 * acc, acc_ph, abort_flag))) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + acc * kTileN + (static_cast<uint32_t>(quad * 32) << 16);
+      // pass 1: row maximum over the visible columns of this tile
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c8 = 0; c8 < kTileN / 32; ++c8) {
+        uint32_t v[32];
+        tmem_ld32(taddr + c8 * 32, v);
+        tc_wait_ld();
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+          const int c = c8 * 32 + k;
+          const float x = __uint_as_float(v[k]);
+          if (c >= clo && c <= chi) mx = fmaxf(mx, x);
+        }
+      }
+      const float m_scaled = mx * g.scale_log2;           // scale > 0
+      // pass 2: exp2 and sums over groups of RBS columns
+      const bool row_ok = i < g.rows_total;
+      float* prow = partial + (static_cast<size_t>(bh) * g.rows_total + (row_ok ? i : 0)) * g.kb_total;
+      const int kb0 = nt * kGroups;
+#pragma unroll 1
+      for (int c8 = 0; c8 < kTileN / 32; ++c8) {
+        uint32_t v[32];
+        tmem_ld32(taddr + c8 * 32, v);
+        tc_wait_ld();
+        if (c8 == kTileN / 32 - 1) {
+          // all TMEM reads of this accumulator are done: hand it back to the MMA thread
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(tempty0 + 8 * acc);
+        }
+        float gs[32 / RBS];
+#pragma unroll
+        for (int q = 0; q < 32 / RBS; ++q) gs[q] = 0.f;
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+          const int c = c8 * 32 + k;
+          const float x = fmaf(__uint_as_float(v[k]), g.scale_log2, -m_scaled);
+          const float p = (c >= clo && c <= chi) ? fast_exp2(x) : 0.f;
+          gs[k / RBS] += p;
+        }
+        if (row_ok) {
+#pragma unroll
+          for (int q = 0; q < 32 / RBS; ++q) {
+            const int kb = kb0 + c8 * (32 / RBS) + q;
+            if (kb < g.kb_total) prow[kb] = gs[q];
+          }
+        }
+      }
+      if (row_ok) mtile[(static_cast<size_t>(bh) * g.rows_total + i) * g.n_ntiles + nt] = m_scaled;
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    // give copies and MMAs still in flight time to land before shared/tensor memory is released
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000) { __nanosleep(1000); }
+    if (threadIdx.x == 0 && status) atomicExch(status, static_cast<int>(kDevWaitTimeout));
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// One block per (query block, head): normalise the partial sums.
+__global__ void __launch_bounds__(128)
+est_finalize_kernel(const EstGeom g, const int* __restrict__ tile_lo, const int* __restrict__ tile_prefix,
+                    const float* __restrict__ partial, const float* __restrict__ mtile, float* __restrict__ sums) {
+  __shared__ float row_m[32];
+  __shared__ float row_linv[32];
+  const int qb = blockIdx.x, bh = blockIdx.y;
+  const int i0 = qb * g.rbs;
+  const int mt = i0 / kTileM;
+  const int nlo = tile_lo[mt];
+  const int ncnt = tile_prefix[mt + 1] - tile_prefix[mt];
+  const int gpt = kTileN / g.rbs;                         // key blocks per tile
+  const int kb_lo = nlo * gpt;
+  int kb_hi = (nlo + ncnt) * gpt;                         // exclusive
+  if (kb_hi > g.kb_total) kb_hi = g.kb_total;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int row = warp; row < g.rbs; row += 4) {
+    const int i = i0 + row;
+    const float* mrow = mtile + (static_cast<size_t>(bh) * g.rows_total + i) * g.n_ntiles;
+    const float* prow = partial + (static_cast<size_t>(bh) * g.rows_total + i) * g.kb_total;
+    float m = -INFINITY;
+    if (i < g.rows_valid)
+      for (int t = lane; t < ncnt; t += 32) m = fmaxf(m, mrow[nlo + t]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    float l = 0.f;
+    if (i < g.rows_valid && m > -INFINITY)
+      for (int kb = kb_lo + lane; kb < kb_hi; kb += 32) {
+        const float mt_ = mrow[kb / gpt];
+        if (mt_ > -INFINITY) l += prow[kb] * exp2f(mt_ - m);
+      }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+    if (lane == 0) {
+      row_m[row] = m;
+      row_linv[row] = l > 0.f ? 1.f / l : 0.f;
+    }
+  }
+  __syncthreads();
+  float* out = sums + (static_cast<size_t>(bh) * g.qb_total + qb) * g.kb_total;
+  for (int kb = threadIdx.x; kb < g.kb_total; kb += blockDim.x) {
+    float acc = 0.f;
+    if (kb >= kb_lo && kb < kb_hi) {
+      for (int row = 0; row < g.rbs; ++row) {
+        const float linv = row_linv[row];
+        if (linv == 0.f) continue;
+        const size_t ri = static_cast<size_t>(bh) * g.rows_total + i0 + row;
+        const float mt_ = mtile[ri * g.n_ntiles + kb / gpt];
+        if (mt_ > -INFINITY) acc += partial[ri * g.kb_total + kb] * exp2f(mt_ - row_m[row]) * linv;
+      }
+    }
+    out[kb] = acc;
+  }
+}
+
+// x = hi + mid + lo in bf16; rows widened to 6*D (see the header).
+__global__ void split_f32_kernel(const float* __restrict__ x, int heads, int len, int D, int64_t sb, int64_t sh,
+                                 int64_t sl, int role, __nv_bfloat16* __restrict__ out, size_t total) {
+  for (size_t e = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; e < total;
+       e += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const int d = static_cast<int>(e % D);
+    size_t rest = e / D;
+    const int l = static_cast<int>(rest % len);
+    rest /= len;
+    const int h = static_cast<int>(rest % heads);
+    const int b = static_cast<int>(rest / heads);
+    const float v = x[b * sb + h * sh + l * sl + d];
+    const __nv_bfloat16 hi = __float2bfloat16_rn(v);
+    const float r1 = v - __bfloat162float(hi);
+    const __nv_bfloat16 mid = __float2bfloat16_rn(r1);
+    const __nv_bfloat16 lo = __float2bfloat16_rn(r1 - __bfloat162float(mid));
+    __nv_bfloat16* o = out + (e / D) * (6 * static_cast<size_t>(D)) + d;
+    if (role == 0) {
+      o[0] = hi; o[D] = hi; o[2 * D] = mid; o[3 * D] = hi; o[4 * D] = lo; o[5 * D] = mid;
+    } else {
+      o[0] = hi; o[D] = mid; o[2 * D] = hi; o[3 * D] = lo; o[4 * D] = hi; o[5 * D] = mid;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------ host side
+struct EstWorkspace {
+  size_t off_tile_lo, off_tile_prefix, off_mtile, off_partial, total;
+};
+
+static int fill_geometry(int batch, int hq, int hkv, int q_len, int k_len, int head_dim, int stride, int block_size,
+                         int chunk_size, float scale, int causal, int semantics, EstGeom& g) {
+  if (batch < 1 || hq < 1 || hkv < 1 || hq % hkv != 0 || q_len < 1 || k_len < 1) return XATTN_B200_ERR_ARG;
+  if (stride != 4 && stride != 8 && stride != 16 && stride != 32) return XATTN_B200_ERR_ARG;
+  if (block_size != 128 || chunk_size < block_size || chunk_size % block_size != 0) return XATTN_B200_ERR_ARG;
+  if (head_dim < kTileK || head_dim % kTileK != 0) return XATTN_B200_ERR_ARG;
+  if (q_len % stride != 0 || k_len % stride != 0) return XATTN_B200_ERR_ARG;
+  const int k_pad = (chunk_size - k_len % chunk_size) % chunk_size;
+  const int q_pad = (chunk_size - q_len % chunk_size) % chunk_size;
+  const int lq = q_len + q_pad, lk = k_len + k_pad;
+  if (lk / chunk_size < lq / chunk_size) return XATTN_B200_ERR_ARG;   // Xattention.py:39
+  g.batch = batch; g.hq = hq; g.hkv = hkv;
+  g.S = stride; g.d_chunks = head_dim / kTileK;
+  g.rows_total = lq / stride; g.cols_total = lk / stride;
+  g.rows_valid = g.rows_total - q_pad / stride;
+  g.cols_valid = g.cols_total - k_pad / stride;
+  g.rcs = chunk_size / stride;
+  g.row_off = (lk / chunk_size - lq / chunk_size) * g.rcs;
+  g.causal = causal ? 1 : 0;
+  g.left_blank = (causal && semantics == XATTN_B200_SEMANTICS_TORCH && k_pad / stride == 0) ? 1 : 0;
+  g.rbs = block_size / stride;
+  g.kb_total = lk / block_size; g.qb_total = lq / block_size;
+  g.n_mtiles = (g.rows_total + kTileM - 1) / kTileM;
+  g.n_ntiles = (g.cols_total + kTileN - 1) / kTileN;
+  g.scale_log2 = scale * 1.4426950408889634f;
+  return XATTN_B200_OK;
+}
+
+static EstWorkspace workspace_layout(const EstGeom& g) {
+  EstWorkspace w;
+  auto up = [](size_t x) { return (x + 255) & ~size_t(255); };
+  size_t o = 0;
+  w.off_tile_lo = o; o = up(o + sizeof(int) * g.n_mtiles);
+  w.off_tile_prefix = o; o = up(o + sizeof(int) * (g.n_mtiles + 1));
+  const size_t rows = static_cast<size_t>(g.batch) * g.hq * g.rows_total;
+  w.off_mtile = o; o = up(o + sizeof(float) * rows * g.n_ntiles);
+  w.off_partial = o; o = up(o + sizeof(float) * rows * g.kb_total);
+  w.total = o;
+  return w;
+}
+
+size_t estimate_workspace_bytes(int batch, int hq, int q_len, int k_len, int stride, int block_size, int chunk_size) {
+  EstGeom g;
+  const int ql = (q_len + stride - 1) / stride * stride, kl = (k_len + stride - 1) / stride * stride;
+  if (fill_geometry(batch, hq, hq, ql, kl, 128, stride, block_size, chunk_size, 1.f, 1, 0, g) != XATTN_B200_OK) return 0;
+  return workspace_layout(g).total;
+}
+
+int estimate_launch(const void* q, const void* k, int dtype, int batch, int hq, int hkv, int q_len, int k_len,
+                    int head_dim, int64_t qsb, int64_t qsh, int64_t qsl, int64_t ksb, int64_t ksh, int64_t ksl,
+                    int stride, int block_size, int chunk_size, float scale, int causal, int semantics,
+                    float* attn_sums, void* workspace, size_t workspace_bytes, int* status, cudaStream_t stream) {
+  if (!q || !k || !attn_sums) return XATTN_B200_ERR_ARG;
+  if (dtype != XATTN_B200_BF16 && dtype != XATTN_B200_F16) return XATTN_B200_ERR_ARG;
+  if (semantics != XATTN_B200_SEMANTICS_TORCH && semantics != XATTN_B200_SEMANTICS_TRITON) return XATTN_B200_ERR_ARG;
+  if (!(scale > 0.f)) return XATTN_B200_ERR_ARG;
+  EstGeom g;
+  int rc = fill_geometry(batch, hq, hkv, q_len, k_len, head_dim, stride, block_size, chunk_size, scale, causal,
+                         semantics, g);
+  if (rc) return rc;
+  const EstWorkspace w = workspace_layout(g);
+  if (!workspace || workspace_bytes < w.total) return XATTN_B200_ERR_WORKSPACE;
+  if ((rc = check_sm100())) return rc;
+  if (g.n_mtiles > 8192) return XATTN_B200_ERR_LIMIT;
+
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  int* tile_lo = reinterpret_cast<int*>(ws + w.off_tile_lo);
+  int* tile_prefix = reinterpret_cast<int*>(ws + w.off_tile_prefix);
+  float* mtile = reinterpret_cast<float*>(ws + w.off_mtile);
+  float* partial = reinterpret_cast<float*>(ws + w.off_partial);
+
+  // 5-D views [head_dim, S, len/S, heads, batch] whose second coordinate picks the token inside a stride group
+  CUtensorMap tmQ, tmK;
+  {
+    const uint64_t dims[5] = {(uint64_t)head_dim, (uint64_t)stride, (uint64_t)(q_len / stride), (uint64_t)hq,
+                              (uint64_t)batch};
+    const uint64_t str[4] = {(uint64_t)qsl * 2, (uint64_t)qsl * 2 * stride, (uint64_t)qsh * 2, (uint64_t)qsb * 2};
+    const uint32_t box[5] = {kTileK, 1, kTileM, 1, 1};
+    if ((rc = make_tmap_16bit(&tmQ, q, 5, dims, str, box))) return rc;
+  }
+  {
+    const uint64_t dims[5] = {(uint64_t)head_dim, (uint64_t)stride, (uint64_t)(k_len / stride), (uint64_t)hkv,
+                              (uint64_t)batch};
+    const uint64_t str[4] = {(uint64_t)ksl * 2, (uint64_t)ksl * 2 * stride, (uint64_t)ksh * 2, (uint64_t)ksb * 2};
+    const uint32_t box[5] = {kTileK, 1, kTileN, 1, 1};
+    if ((rc = make_tmap_16bit(&tmK, k, 5, dims, str, box))) return rc;
+  }
+
+  est_setup_kernel<<<1, 256, sizeof(int) * g.n_mtiles, stream>>>(g, tile_lo, tile_prefix);
+  if ((rc = launch_status())) return rc;
+
+  const uint32_t idesc = make_idesc_f16(kTileM, kTileN, dtype == XATTN_B200_BF16, false, false);
+  const int grid = sm_count();
+  auto launch = [&](auto kern) -> int {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem) != cudaSuccess)
+      return XATTN_B200_ERR_CUDA;
+    kern<<<grid, kGemmThreads, kGemmSmem, stream>>>(tmQ, tmK, g, tile_lo, tile_prefix, partial, mtile, idesc, status);
+    return launch_status();
+  };
+  switch (g.rbs) {
+    case 4: rc = launch(est_gemm_kernel<4>); break;
+    case 8: rc = launch(est_gemm_kernel<8>); break;
+    case 16: rc = launch(est_gemm_kernel<16>); break;
+    case 32: rc = launch(est_gemm_kernel<32>); break;
+    default: rc = XATTN_B200_ERR_ARG;
+  }
+  if (rc) return rc;
+
+  est_finalize_kernel<<<dim3(g.qb_total, batch * hq), 128, 0, stream>>>(g, tile_lo, tile_prefix, partial, mtile,
+                                                                        attn_sums);
+  return launch_status();
+}
+
+int split_f32_launch(const float* x, int batch, int heads, int len, int head_dim, int64_t sb, int64_t sh, int64_t sl,
+                     int role, void* out, cudaStream_t stream) {
+  if (!x || !out || batch < 1 || heads < 1 || len < 1 || head_dim < 1 || (role != 0 && role != 1))
+    return XATTN_B200_ERR_ARG;
+  const size_t total = static_cast<size_t>(batch) * heads * len * head_dim;
+  const int block = 256;
+  size_t blocks = (total + block - 1) / block;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  split_f32_kernel<<<static_cast<int>(blocks), block, 0, stream>>>(x, heads, len, head_dim, sb, sh, sl, role,
+                                                                    static_cast<__nv_bfloat16*>(out), total);
+  return launch_status();
+}
+
+}  // namespace xb
