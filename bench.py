@@ -118,14 +118,15 @@ def sum_over_ranks(x: float, dist, device) -> float:
 
 
 # ------------------------------------------------------------------------------------ CPU arm
-def cpu_reference_sample(q, k, v, w, chunk, q_blocks_sampled=8):
+def cpu_reference_sample(q, k, v, w, chunk, q_blocks_sampled=64, head=0):
     """One bounded sample of the reference's CPU path on ONE query head: the full-length estimate and
     selection of that head (Xattention.py:13-299 restated in oracle/), then dense masked attention
     (the fp32 statement of the attention phase) for `q_blocks_sampled` evenly spaced query blocks.
-    Returns (seconds, dense-equivalent FLOPs covered)."""
+    Returns (seconds per head, dense-equivalent FLOPs of a head, detail)."""
     from oracle import xattn_oracle as orc
     rep = q.shape[1] // k.shape[1]
-    q1, k1, v1 = q[:, :1].float(), k[:, :1].float(), v[:, :1].float()
+    hk = head // rep
+    q1, k1, v1 = q[:, head:head + 1].float(), k[:, hk:hk + 1].float(), v[:, hk:hk + 1].float()
     L = q.shape[2]
     t0 = time.perf_counter()
     _, mask = orc.xattn_estimate_oracle(q1, k1, 128, w.stride, 1.0, w.threshold, chunk, w.causal)
@@ -291,12 +292,19 @@ def run_gpu_arm(args):
     cpu_baseline = None
     if rank == 0 and n == 1 and not args.no_cpu_baseline:
         torch.set_num_threads(os.cpu_count() or 1)
-        t_head, _, detail = cpu_reference_sample(q, k, v, w, chunk, args.cpu_q_blocks)
+        rep_ = w.hq // w.hkv
+        t_heads = []
+        for hh in range(0, w.hq, rep_):          # one query head per kv group
+            t_h, _, detail = cpu_reference_sample(q, k, v, w, chunk, args.cpu_q_blocks, head=hh)
+            t_heads.append(t_h)
+        t_head = sum(t_heads) / len(t_heads)
+        detail["heads_sampled"] = len(t_heads)
         cpu_value = effective_flops(w) / (t_head * w.hq) / 1e12
         cpu_baseline = dict(
             value=cpu_value, unit=UNIT, cores=torch.get_num_threads(), kind="port",
-            sample=(f"1 of {w.hq} query heads at full length: estimate+select in full, dense masked attention on "
-                    f"{detail['q_blocks']} evenly spaced query blocks scaled to the head; x {w.hq} heads"),
+            sample=(f"{detail['heads_sampled']} of {w.hq} query heads at full length: estimate+select in full, dense "
+                    f"masked attention on {detail['q_blocks']} evenly spaced query blocks scaled to the head; "
+                    f"mean per-head time x {w.hq} heads"),
             host_cores=os.cpu_count(), detail=detail)
 
     if rank == 0:
@@ -325,7 +333,7 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--cpu-q-blocks", type=int, default=8)
+    ap.add_argument("--cpu-q-blocks", type=int, default=64)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":
