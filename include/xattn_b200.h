@@ -88,6 +88,35 @@ int xattn_b200_estimate(const void* q, const void* k, int dtype, int batch, int 
                         size_t workspace_bytes, int* status, void* cuda_stream);
 
 /*
+ * The estimate without a caller-supplied workspace.  No counterpart in the reference.
+ *
+ * Meant for callers that cannot allocate device memory where they call the estimate: a process whose
+ * GPU memory was handed out at start-up to a pool that this caller does not own, a plugin host that
+ * forbids allocation after initialisation, or a latency-critical section where an allocation (and the
+ * device synchronisation it can imply) is not acceptable.  The scratch that xattn_b200_estimate takes
+ * from the caller lives here in a fixed array inside the library image, XATTN_B200_STATIC_SCRATCH_BYTES
+ * large, resident on every GPU that loads the library until the process exits.  The call itself
+ * allocates and frees nothing; the caller still provides q, k and attn_sums.
+ *
+ * Arguments and results are those of xattn_b200_estimate (minus workspace/workspace_bytes).
+ * Returns XATTN_B200_ERR_LIMIT when xattn_b200_estimate_workspace_bytes(...) for the problem exceeds
+ * XATTN_B200_STATIC_SCRATCH_BYTES -- use xattn_b200_estimate with your own workspace then.
+ *
+ * The first call on each device looks up the array's device address (the device must be current, as
+ * for every call); make that first call outside any CUDA stream capture.  All calls on a device share
+ * the one array, which simply keeps whatever the last call left in it (no call relies on its previous
+ * contents): two calls whose kernels can overlap on the GPU -- different streams without an ordering
+ * between them, or several host threads -- race on it and give wrong sums.  Order them on one stream
+ * or with events.
+ */
+#define XATTN_B200_STATIC_SCRATCH_BYTES (32u << 20)
+int xattn_b200_estimate_static(const void* q, const void* k, int dtype, int batch, int hq, int hkv, int q_len,
+                               int k_len, int head_dim, int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_l,
+                               int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_l, int stride,
+                               int block_size, int chunk_size, float scale, int causal, int semantics,
+                               float* attn_sums, int* status, void* cuda_stream);
+
+/*
  * Split fp32 rows into three bf16 terms (x = hi + mid + lo) laid out as rows of 6*head_dim so that
  * a bf16 GEMM over the widened rows reproduces the fp32 product to ~2^-24:
  *   role 0 (query side): [hi, hi, mid, hi, lo, mid]     role 1 (key side): [hi, mid, hi, lo, hi, mid]

@@ -24,6 +24,8 @@ SIGNATURES = {
     "xattn_b200_estimate_workspace_bytes": (_sz, [_i, _i, _i, _i, _i, _i, _i]),
     "xattn_b200_estimate": (_i, [_p, _p, _i, _i, _i, _i, _i, _i, _i, _i64, _i64, _i64, _i64, _i64, _i64,
                                  _i, _i, _i, _f, _i, _i, _p, _p, _sz, _p, _p]),
+    "xattn_b200_estimate_static": (_i, [_p, _p, _i, _i, _i, _i, _i, _i, _i, _i64, _i64, _i64, _i64, _i64, _i64,
+                                        _i, _i, _i, _f, _i, _i, _p, _p, _p]),
     "xattn_b200_split_f32": (_i, [_p, _i, _i, _i, _i, _i64, _i64, _i64, _i, _p, _p]),
     "xattn_b200_select": (_i, [_p, _i, _i, _i, _i, _i, _i, _i, _i, _d, _p, _i, _i, _p, _p, _p,
                                _i, _i, _i, _i, _p, _p]),
