@@ -130,6 +130,32 @@ def test_select_vs_find_blocks_chunked_fixtures():
         assert not d.any(), (i, spec, d.nonzero()[:5].tolist())
 
 
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("N,bpc", [(512, 16), (1024, 64), (200, 8)])
+def test_select_flat_rows_take_the_sort_route(causal, N, bpc):
+    """Flat score rows keep hundreds of blocks, which exercises the warp-sort route of the kernel (peaked
+    rows finish in the extraction loop); both must agree with the oracle outside the margin."""
+    from xattn_b200 import ops
+    g = torch.Generator().manual_seed(N + bpc)
+    R = 2 * bpc
+    off = N - R
+    x = torch.rand(1, 3, R, N, generator=g) + 0.05
+    x[:, 1] = x[:, 1] ** 8                       # one peaked head next to two flat ones
+    if causal:
+        x = x * (torch.arange(N)[None, :] <= off + torch.arange(R)[:, None]).float()
+    for thr in (0.3, 0.9, 1.0):
+        got, _, _ = ops.select_blocks(x.to(DEV), bpc, off, thr, causal, True)
+        parts, exs = [], []
+        for c in range(2):
+            xc = x[:, :, c * bpc:(c + 1) * bpc]
+            parts.append(orc.select_blocks_chunk(xc, off + c * bpc, thr, causal))
+            exs.append(orc.margin_exempt_chunk(xc, off + c * bpc, thr, causal))
+        want = orc.finish_masks(torch.cat(parts, -2), R, causal, False, False)
+        dmask = (got.cpu() != want) & ~torch.cat(exs, -2)
+        assert not dmask.any(), (thr, dmask.nonzero()[:5].tolist())
+        assert int(want.sum()) > 24 * 3 * R * (0.5 if causal else 1.0) or thr < 0.9
+
+
 def test_select_lists_match_mask():
     from xattn_b200 import ops
     g = torch.Generator().manual_seed(9)

@@ -3,10 +3,13 @@
 // Reference: find_blocks_chunked, xattn/src/utils.py:87-172 (+ :176-180), called per query chunk by
 // xattn_estimate (xattn/src/Xattention.py:255-263), and the post-processing at
 // xattn/src/Xattention.py:275-297.  The reference sorts every row twice in fp64 with torch.sort,
-// builds cumulative sums with cat/cumsum and scatters; here one thread block owns one
-// (head, query-block) row: a bitonic sort of (score, index) keys in shared memory, an fp64 prefix
-// scan, the take/skip decision per rank, then the mask row and the compacted ascending block list
-// that the attention kernel walks.
+// builds cumulative sums with cat/cumsum and scatters, once per chunk with two host syncs.  Here one
+// launch covers all chunks and one WARP owns one (head, query-block) row, staged in shared memory.
+// Attention rows are peaked, so the kept set is small: the warp extracts the largest remaining score
+// (lowest index on ties) one at a time, accumulating the prefix in fp64 exactly as the rule is
+// stated, and stops at the first rank that is not taken.  Rows that are still going after
+// kPeelMax extractions (flat score rows) switch to a warp-level bitonic sort of what is left plus
+// an fp64 prefix scan.  Both routes apply the same rule, so the result does not depend on the route.
 //
 // Rule per row R (chunk c = R / bpc, current_index cur = block_offset + c*bpc, diagonal d = cur + R%bpc),
 // scores x[0..N) taken as fp64, req = sum(x) * threshold:
@@ -21,7 +24,7 @@
 
 namespace xb {
 
-constexpr int kSelThreads = 256;
+constexpr int kPeelMax = 24;
 
 struct SelParams {
   int batch, heads, q_blocks, k_blocks;
@@ -29,7 +32,10 @@ struct SelParams {
   double threshold;
   int keep_sink, keep_recent;
   int list_q_blocks, list_k_blocks, list_q_len, list_k_len;
-  int np2;   // k_blocks rounded up to a power of two
+  int np2;            // k_blocks rounded up to a power of two (>= 32)
+  int warps_per_cta;
+  int vals_bytes, keys_bytes, per_warp_bytes;
+  int rows_total;
 };
 
 __device__ __forceinline__ bool list_keeps(int causal, int R, int j, int list_q_len, int list_k_len) {
@@ -40,127 +46,148 @@ __device__ __forceinline__ bool list_keeps(int causal, int R, int j, int list_q_
   return static_cast<long long>(j) * 128 <= static_cast<long long>(last_q) + (list_k_len - list_q_len);
 }
 
-__global__ void __launch_bounds__(kSelThreads)
-select_kernel(const float* __restrict__ sums, const SelParams p, const float* __restrict__ thr_per_head,
-              uint8_t* __restrict__ mask_out, int32_t* __restrict__ idx_out, int32_t* __restrict__ cnt_out) {
-  extern __shared__ __align__(16) uint8_t sel_smem[];
-  unsigned long long* keys = reinterpret_cast<unsigned long long*>(sel_smem);       // [np2]
-  double* scan = reinterpret_cast<double*>(sel_smem + sizeof(unsigned long long) * p.np2);  // [np2]
-  uint8_t* mrow = reinterpret_cast<uint8_t*>(scan + p.np2);                          // [k_blocks]
-  __shared__ double s_red[kSelThreads / 32];
-  __shared__ double s_total, s_forced;
-  __shared__ int s_untaken, s_count;
-  __shared__ int s_wsum[kSelThreads / 32];
+__device__ __forceinline__ double warp_sum(double v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
 
-  const int R = blockIdx.x;
-  const int bh = blockIdx.y;
+__global__ void select_kernel(const float* __restrict__ sums, const SelParams p,
+                              const float* __restrict__ thr_per_head, uint8_t* __restrict__ mask_out,
+                              int32_t* __restrict__ idx_out, int32_t* __restrict__ cnt_out) {
+  extern __shared__ __align__(16) uint8_t sel_smem[];
+  const int lane = threadIdx.x & 31;
+  const int wib = threadIdx.x >> 5;
+  const int w = blockIdx.x * p.warps_per_cta + wib;
+  if (w >= p.rows_total) return;                         // whole warps leave; no block-wide barrier below
+  uint8_t* base_ptr = sel_smem + static_cast<size_t>(wib) * p.per_warp_bytes;
+  float* vals = reinterpret_cast<float*>(base_ptr);                                  // [N]  (-1 = removed)
+  unsigned long long* keys = reinterpret_cast<unsigned long long*>(base_ptr + p.vals_bytes);      // [np2]
+  uint8_t* mrow = base_ptr + p.vals_bytes + p.keys_bytes;                            // [N]
+
+  const int bh = w / p.q_blocks;
+  const int R = w - bh * p.q_blocks;
   const int h = bh % p.heads;
   const int N = p.k_blocks;
-  const int tid = threadIdx.x;
-  const float* x = sums + (static_cast<size_t>(bh) * p.q_blocks + R) * N;
+  const float* x = sums + static_cast<size_t>(w) * N;
 
   const int cur = p.block_offset + (R / p.bpc) * p.bpc;
   const int d = cur + R % p.bpc;
   const bool f0 = p.causal && cur != 0;            // block 0 forced
   const int n_forced = p.causal ? (f0 ? 2 : 1) : 0;
   const int lag = n_forced == 1 ? 1 : 0;
+  const int n_others = N - n_forced;
 
-  // keys + total
   double part = 0.0, fpart = 0.0;
-  for (int j = tid; j < p.np2; j += kSelThreads) {
-    unsigned long long key = 0ull;
-    if (j < N) {
-      const float v = x[j];
-      part += static_cast<double>(v);
-      const bool forced = p.causal && (j == d || (f0 && j == 0));
-      if (forced) fpart += static_cast<double>(v);
-      else {
-        const float vc = v > 0.f ? v : 0.f;
-        key = (static_cast<unsigned long long>(__float_as_uint(vc)) << 32) | (0xFFFFFFFFull - static_cast<unsigned>(j));
-      }
-      mrow[j] = forced ? 1 : 0;
-    }
-    keys[j] = key;
+  for (int j = lane; j < N; j += 32) {
+    const float v = x[j];
+    part += static_cast<double>(v);
+    const bool forced = p.causal && (j == d || (f0 && j == 0));
+    if (forced) fpart += static_cast<double>(v);
+    vals[j] = forced ? -1.f : (v > 0.f ? v : 0.f);
+    mrow[j] = forced ? 1 : 0;
   }
-  // block reductions (fp64)
-  for (int pass = 0; pass < 2; ++pass) {
-    double v = pass == 0 ? part : fpart;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    if ((tid & 31) == 0) s_red[tid >> 5] = v;
-    __syncthreads();
-    if (tid == 0) {
-      double t = 0.0;
-      for (int w = 0; w < kSelThreads / 32; ++w) t += s_red[w];
-      if (pass == 0) s_total = t; else s_forced = t;
-      s_untaken = 0;
-    }
-    __syncthreads();
-  }
+  const double total = warp_sum(part);
+  const double fsum = warp_sum(fpart);
   const double thr = thr_per_head ? static_cast<double>(thr_per_head[h]) : p.threshold;
-  const double req = s_total * thr;
-  const double fsum = s_forced;
+  const double req = total * thr;
+  __syncwarp();
 
-  // bitonic sort, descending
-  for (int k = 2; k <= p.np2; k <<= 1) {
-    for (int j = k >> 1; j > 0; j >>= 1) {
-      for (int t = tid; t < p.np2; t += kSelThreads) {
-        const int ixj = t ^ j;
-        if (ixj > t) {
-          const unsigned long long a = keys[t], b = keys[ixj];
-          const bool desc = (t & k) == 0;
-          if (desc ? (a < b) : (a > b)) { keys[t] = b; keys[ixj] = a; }
+  bool untaken = !(req > 0.0);                     // the leading slots of the reference compare 0 < req too
+  if (req > 0.0) {
+    int i = 1;                                     // rank being decided
+    double s_cur = 0.0, s_lag = 0.0;               // prefix[i-1], prefix[max(i-2,0)] of the ranked scores
+    bool sort_rest = false;
+    while (i <= n_others) {
+      const double c = lag ? (i == 1 ? 0.0 : fsum + s_lag) : fsum + s_cur;
+      if (!(c < req)) { untaken = true; break; }
+      if (i > kPeelMax) { sort_rest = true; break; }
+      // largest remaining score, lowest index on ties
+      float bv = -1.f;
+      int bj = 0x7fffffff;
+      for (int j = lane; j < N; j += 32) {
+        const float v = vals[j];
+        if (v > bv) { bv = v; bj = j; }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oj = __shfl_xor_sync(0xffffffffu, bj, o);
+        if (ov > bv || (ov == bv && oj < bj)) { bv = ov; bj = oj; }
+      }
+      if (bv == 0.f && fsum + s_cur < req) {
+        // only zero scores are left and the prefix no longer moves: every remaining rank is taken
+        for (int j = lane; j < N; j += 32)
+          if (vals[j] == 0.f) mrow[j] = 1;
+        i = n_others + 1;
+        break;
+      }
+      if (lane == (bj & 31)) { vals[bj] = -1.f; mrow[bj] = 1; }
+      __syncwarp();
+      s_lag = s_cur;
+      s_cur += static_cast<double>(bv);
+      ++i;
+    }
+    if (sort_rest) {
+      // ranks i.. : sort what is left (descending score, ascending index), fp64 prefix, decide per rank
+      for (int t = lane; t < p.np2; t += 32) {
+        unsigned long long key = 0ull;
+        if (t < N && vals[t] >= 0.f)
+          key = (static_cast<unsigned long long>(__float_as_uint(vals[t])) << 32) | (0xFFFFFFFFull - static_cast<unsigned>(t));
+        keys[t] = key;
+      }
+      __syncwarp();
+      for (int k = 2; k <= p.np2; k <<= 1) {
+        for (int j = k >> 1; j > 0; j >>= 1) {
+          for (int t = lane; t < p.np2; t += 32) {
+            const int ixj = t ^ j;
+            if (ixj > t) {
+              const unsigned long long a = keys[t], b = keys[ixj];
+              const bool desc = (t & k) == 0;
+              if (desc ? (a < b) : (a > b)) { keys[t] = b; keys[ixj] = a; }
+            }
+          }
+          __syncwarp();
         }
       }
-      __syncthreads();
+      const int n_rem = n_others - (i - 1);
+      const int seg = p.np2 / 32;                  // contiguous positions per lane
+      const int t0 = lane * seg;
+      double local = 0.0;
+      for (int t = t0; t < t0 + seg; ++t) local += static_cast<double>(__uint_as_float(static_cast<unsigned>(keys[t] >> 32)));
+      double incl = local;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const double up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+      }
+      double running = incl - local;               // sum of the sorted scores before position t0
+      int ut = 0;
+      for (int t = t0; t < t0 + seg && t < n_rem; ++t) {
+        const unsigned long long key = keys[t];
+        const double v = static_cast<double>(__uint_as_float(static_cast<unsigned>(key >> 32)));
+        double c;
+        if (!lag) c = fsum + s_cur + running;                       // prefix[rank-1]
+        else if (t == 0) c = fsum + s_lag;                          // prefix[rank-2], rank = i
+        else c = fsum + s_cur + (running - static_cast<double>(__uint_as_float(static_cast<unsigned>(keys[t - 1] >> 32))));
+        if (c < req) mrow[0xFFFFFFFFu - static_cast<unsigned>(key & 0xFFFFFFFFull)] = 1;
+        else ut = 1;
+        running += v;
+      }
+      if (__any_sync(0xffffffffu, ut)) untaken = true;
     }
   }
-
-  // inclusive fp64 scan of the ranked scores
-  for (int t = tid; t < p.np2; t += kSelThreads)
-    scan[t] = static_cast<double>(__uint_as_float(static_cast<unsigned>(keys[t] >> 32)));
-  __syncthreads();
-  for (int off = 1; off < p.np2; off <<= 1) {
-    double tmp[32];   // np2 <= 8192 -> at most 32 elements per thread
-    int c = 0;
-    for (int t = tid; t < p.np2; t += kSelThreads, ++c) tmp[c] = t >= off ? scan[t - off] : 0.0;
-    __syncthreads();
-    c = 0;
-    for (int t = tid; t < p.np2; t += kSelThreads, ++c) scan[t] += tmp[c];
-    __syncthreads();
-  }
-
-  // decisions per rank position
-  const int n_others = N - n_forced;
-  int untaken = 0;
-  for (int t = tid; t < n_others; t += kSelThreads) {
-    const int i = t + 1;
-    double c;
-    if (i - lag <= 0) c = 0.0;
-    else {
-      const int m = i - lag - 1;           // number of ranked scores summed
-      c = fsum + (m >= 1 ? scan[m - 1] : 0.0);
-    }
-    if (c < req) {
-      const unsigned j = 0xFFFFFFFFu - static_cast<unsigned>(keys[t] & 0xFFFFFFFFull);
-      mrow[j] = 1;
-    } else {
-      untaken = 1;
-    }
-  }
-  if (!(req > 0.0)) untaken = 1;           // the forced slots of the reference compare 0 < req too
-  if (untaken) s_untaken = 1;
-  __syncthreads();
-  if (tid == 0 && s_untaken) mrow[0] = 1;
-  __syncthreads();
+  __syncwarp();
+  if (untaken && lane == 0) mrow[0] = 1;
+  __syncwarp();
 
   // post-processing + outputs
   const bool want_list = idx_out && cnt_out && R < p.list_q_blocks;
   int32_t* lrow = want_list ? idx_out + (static_cast<size_t>(bh) * p.list_q_blocks + R) * p.list_k_blocks : nullptr;
-  uint8_t* mo = mask_out ? mask_out + (static_cast<size_t>(bh) * p.q_blocks + R) * N : nullptr;
+  uint8_t* mo = mask_out ? mask_out + static_cast<size_t>(w) * N : nullptr;
   int base = 0;
-  for (int j0 = 0; j0 < N; j0 += kSelThreads) {
-    const int j = j0 + tid;
+  for (int j0 = 0; j0 < N; j0 += 32) {
+    const int j = j0 + lane;
     int m = 0;
     if (j < N) {
       m = mrow[j];
@@ -172,21 +199,11 @@ select_kernel(const float* __restrict__ sums, const SelParams p, const float* __
     if (want_list) {
       const int keep = (m && j < p.list_k_blocks && list_keeps(p.causal, R, j, p.list_q_len, p.list_k_len)) ? 1 : 0;
       const unsigned bal = __ballot_sync(0xffffffffu, keep);
-      const int wpre = __popc(bal & ((1u << (tid & 31)) - 1u));
-      if ((tid & 31) == 0) s_wsum[tid >> 5] = __popc(bal);
-      __syncthreads();
-      int woff = 0, tot = 0;
-      for (int w = 0; w < kSelThreads / 32; ++w) {
-        if (w < (tid >> 5)) woff += s_wsum[w];
-        tot += s_wsum[w];
-      }
-      if (keep) lrow[base + woff + wpre] = j;
-      base += tot;
-      __syncthreads();
+      if (keep) lrow[base + __popc(bal & ((1u << lane) - 1u))] = j;
+      base += __popc(bal);
     }
   }
-  if (want_list && tid == 0) cnt_out[static_cast<size_t>(bh) * p.list_q_blocks + R] = base;
-  (void)s_count;
+  if (want_list && lane == 0) cnt_out[static_cast<size_t>(bh) * p.list_q_blocks + R] = base;
 }
 
 // One warp per (head, query-block) row of a caller-supplied mask.
@@ -234,13 +251,22 @@ int select_launch(const float* attn_sums, int batch, int heads, int q_blocks, in
   int np2 = 32;
   while (np2 < k_blocks) np2 <<= 1;
   p.np2 = np2;
-  const size_t smem = static_cast<size_t>(np2) * 16 + ((k_blocks + 15) & ~15);
+  p.vals_bytes = (k_blocks * 4 + 15) & ~15;
+  p.keys_bytes = np2 * 8;
+  p.per_warp_bytes = p.vals_bytes + p.keys_bytes + ((k_blocks + 15) & ~15);
+  int wpc = (56 * 1024) / p.per_warp_bytes;
+  wpc = wpc < 1 ? 1 : (wpc > 8 ? 8 : wpc);
+  p.warps_per_cta = wpc;
+  const long long rows = static_cast<long long>(batch) * heads * q_blocks;
+  if (rows > 0x7fffffffLL) return XATTN_B200_ERR_LIMIT;
+  p.rows_total = static_cast<int>(rows);
+  const size_t smem = static_cast<size_t>(wpc) * p.per_warp_bytes;
   if (smem > 48 * 1024 &&
       cudaFuncSetAttribute(select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) !=
           cudaSuccess)
     return XATTN_B200_ERR_CUDA;
-  select_kernel<<<dim3(q_blocks, batch * heads), kSelThreads, smem, stream>>>(attn_sums, p, thr_per_head, mask,
-                                                                               block_idx, block_cnt);
+  const int grid = static_cast<int>((rows + wpc - 1) / wpc);
+  select_kernel<<<grid, wpc * 32, smem, stream>>>(attn_sums, p, thr_per_head, mask, block_idx, block_cnt);
   return launch_status();
 }
 
