@@ -63,18 +63,18 @@ __host__ __device__ inline void row_bounds(const EstGeom& g, int i, int& lo, int
 __global__ void est_setup_kernel(EstGeom g, int* __restrict__ tile_lo, int* __restrict__ tile_prefix) {
   extern __shared__ int s_cnt[];
   for (int mt = threadIdx.x; mt < g.n_mtiles; mt += blockDim.x) {
-    int lo_min = 0x7fffffff, hi_max = -1;
-    for (int r = 0; r < kTileM; ++r) {
-      const int i = mt * kTileM + r;
-      if (i >= g.rows_total) break;
+    // lo(i) and hi(i) never decrease with i, so the tile's column range is [lo(first row), hi(last valid row)]
+    const int i0 = mt * kTileM;
+    int i1 = i0 + kTileM;
+    if (i1 > g.rows_total) i1 = g.rows_total;
+    if (i1 > g.rows_valid) i1 = g.rows_valid;
+    int lo_min = 0, hi_max = -1;
+    if (i1 > i0) {
       int lo, hi;
-      row_bounds(g, i, lo, hi);
-      if (hi >= lo) {
-        lo_min = lo < lo_min ? lo : lo_min;
-        hi_max = hi > hi_max ? hi : hi_max;
-      }
+      row_bounds(g, i0, lo_min, hi);
+      row_bounds(g, i1 - 1, lo, hi_max);
     }
-    if (hi_max < 0) {
+    if (hi_max < lo_min) {
       tile_lo[mt] = 0;
       s_cnt[mt] = 0;
     } else {

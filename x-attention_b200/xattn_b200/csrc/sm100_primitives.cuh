@@ -21,6 +21,7 @@ constexpr long long kWaitCycleLimit = 3000000000LL;   // ~1.5 s at 2 GHz; normal
 enum DeviceStatus : int {
   kDevOk = 0,
   kDevWaitTimeout = 101,       // an mbarrier wait ran out
+  kDevBadSmemAlign = 102,      // dynamic shared memory is not 1024-byte aligned
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
