@@ -34,9 +34,10 @@ constexpr int kAttnThreads = 512;
 constexpr int kTile16 = 128 * 128 * 2;     // one 128x128 16-bit tile = two 64-column TMA boxes
 constexpr int kHalf16 = kTile16 / 2;
 constexpr int kAttnSmemTiles = kTile16 * 6;                   // Q, K, V per stream
-constexpr int kSchedCap = 3072;                               // work items one CTA can schedule
+constexpr int kSchedCap = 2048;                               // work items one CTA can schedule
+constexpr int kStageBytes = 4 * 32 * 128;                     // per epilogue warp: 32 rows x 64 16-bit columns
 constexpr int kAttnSmem = kAttnSmemTiles + 2 * 2 * 128 * 4 /*row sums*/ + 256 /*barriers*/ +
-                          3 * kSchedCap * 2 /*schedule*/ + 16;
+                          3 * kSchedCap * 2 /*schedule*/ + 16 + kStageBytes;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 struct AttnParams {
@@ -101,7 +102,11 @@ __device__ __forceinline__ int list_window(const AttnParams& p, const int32_t* _
                                            int n, int j0, int lane) {
   const int e = n - 1 - (j0 + lane);
   if (e < 0) return 0;
-  return __ldg(block_idx + row * p.list_k_blocks + e);
+  // volatile asm pins the issue point: a plain read-only load would be sunk by the compiler to its first use,
+  // which turns the intended prefetch into an exposed memory latency
+  int v;
+  asm volatile("ld.global.nc.s32 %0, [%1];" : "=r"(v) : "l"(block_idx + row * p.list_k_blocks + e));
+  return v;
 }
 
 // Per-CTA schedule, built once in shared memory by the prologue: the block count of every item of this CTA
@@ -159,6 +164,7 @@ block_sparse_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
   uint16_t* sch_seq0 = sch_cnt + kSchedCap;
   uint16_t* sch_seq1 = sch_seq0 + kSchedCap;
   int* sch_total = reinterpret_cast<int*>(sch_seq1 + kSchedCap);
+  uint8_t* stage_base = reinterpret_cast<uint8_t*>(sch_total) + 16;     // 16-byte aligned
   const int G = gridDim.x;
   const int n_local = (p.total_items - static_cast<int>(blockIdx.x) + G - 1) / G;     // host guarantees <= kSchedCap
   for (int i = threadIdx.x; i < n_local; i += kAttnThreads) {
@@ -312,32 +318,34 @@ block_sparse_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
     const int n_items = sch.n_seq[s];
     uint32_t bc = 0;
     bool ok = true;
-    size_t row = n_items > 0 ? decode_item(p, blockIdx.x + sch.seq[s][0] * G).row : 0;
+    Item it = decode_item(p, n_items > 0 ? blockIdx.x + sch.seq[s][0] * G : 0);
     int n = n_items > 0 ? sch.cnt[sch.seq[s][0]] : 0;
-    int win = n_items > 0 ? list_window(p, block_idx, row, n, 0, lane) : 0;
+    int win = n_items > 0 ? list_window(p, block_idx, it.row, n, 0, lane) : 0;
     for (int m = 0; m < n_items && ok; ++m) {
-      const int t = blockIdx.x + sch.seq[s][m] * G;
+      if (threadIdx.x == (s << 7)) XB_TRACE_EV(0x36, m);
       // the stream's next item: fetch its first list window while this one is processed
-      size_t nrow = 0;
+      Item nit = it;
       int nn = 0, nwin = 0;
       if (m + 1 < n_items) {
         const int i2 = sch.seq[s][m + 1];
-        nrow = decode_item(p, blockIdx.x + i2 * G).row;
+        nit = decode_item(p, blockIdx.x + i2 * G);
         nn = sch.cnt[i2];
-        nwin = list_window(p, block_idx, nrow, nn, 0, lane);
+        nwin = list_window(p, block_idx, nit.row, nn, 0, lane);
       }
-      const Item it = decode_item(p, t);
+      const size_t row = it.row;
       const int q_pos = it.qb * 128 + r;
       int row_last = p.k_len - 1;                       // last key position this row may see
       if (p.causal && q_pos + k_off < row_last) row_last = q_pos + k_off;
       float m_used = -INFINITY, l = 0.f;
       int w = win, w_next = list_window(p, block_idx, row, n, 32, lane);
+      if (threadIdx.x == (s << 7)) XB_TRACE_EV(0x37, m);
       for (int j = 0; j < n; ++j, ++bc) {
         if (j > 0 && (j & 31) == 0) {
           w = w_next;
           w_next = list_window(p, block_idx, row, n, j + 32, lane);
         }
         const int k0 = __shfl_sync(0xffffffffu, w, j & 31) * 128;
+        if (threadIdx.x == (s << 7)) XB_TRACE_EV(0x38, bc);
         const int limit = row_last - k0;                // columns c <= limit are visible
         const bool masked = __any_sync(0xffffffffu, limit < 127);
         if (threadIdx.x == (s << 7)) XB_TRACE_EV(0x30, bc);
@@ -345,24 +353,39 @@ block_sparse_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
         if (!__all_sync(0xffffffffu, mbar_wait(s_full, bc & 1, abort_flag))) { ok = false; break; }
         tc_fence_after();
         if (threadIdx.x == (s << 7)) XB_TRACE_EV(0x31, bc);
-        // ---- pass 1: row maximum, 8 independent chains of 3-input max
+        // ---- pass 1: row maximum, 8 independent chains of 3-input max.  In a masked block (diagonal / tail)
+        // each 32-column chunk is classified per warp: all visible, none visible, or mixed (per-element
+        // select).  The chunk loops are kept rolled: the kernel is bound by instruction issue and a small
+        // loop body measured faster than a fully unrolled one.
         float mx8[8];
 #pragma unroll
         for (int q = 0; q < 8; ++q) mx8[q] = -INFINITY;
+        uint32_t cls_mixed = 0u, cls_none = 0u;        // bit c4
+        if (masked) {
 #pragma unroll
+          for (int c4 = 0; c4 < 4; ++c4) {
+            const bool all_vis = __all_sync(0xffffffffu, limit - 32 * c4 >= 31);
+            const bool none_vis = __all_sync(0xffffffffu, limit - 32 * c4 < 0);
+            if (none_vis) cls_none |= 1u << c4;
+            else if (!all_vis) cls_mixed |= 1u << c4;
+          }
+        }
+#pragma unroll 1
         for (int c4 = 0; c4 < 4; ++c4) {
+          if ((cls_none >> c4) & 1u) continue;
           uint32_t v[32];
           tmem_ld32(ts + c4 * 32, v);
           tc_wait_ld();
-          if (!masked) {
+          if (!((cls_mixed >> c4) & 1u)) {
 #pragma unroll
             for (int k = 0; k < 16; ++k)
               mx8[k & 7] = max3(mx8[k & 7], __uint_as_float(v[2 * k]), __uint_as_float(v[2 * k + 1]));
           } else {
+            const int lim4 = limit - 32 * c4;
 #pragma unroll
             for (int k = 0; k < 16; ++k)
-              mx8[k & 7] = max3(mx8[k & 7], (c4 * 32 + 2 * k) <= limit ? __uint_as_float(v[2 * k]) : -INFINITY,
-                                (c4 * 32 + 2 * k + 1) <= limit ? __uint_as_float(v[2 * k + 1]) : -INFINITY);
+              mx8[k & 7] = max3(mx8[k & 7], 2 * k <= lim4 ? __uint_as_float(v[2 * k]) : -INFINITY,
+                                2 * k + 1 <= lim4 ? __uint_as_float(v[2 * k + 1]) : -INFINITY);
           }
         }
         const float mx = fmaxf(max3(mx8[0], mx8[1], mx8[2]), max3(max3(mx8[3], mx8[4], mx8[5]), mx8[6], mx8[7]));
@@ -396,24 +419,40 @@ block_sparse_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
         unsigned long long ls2[4];
 #pragma unroll
         for (int q = 0; q < 4; ++q) ls2[q] = 0ull;     // (+0.f, +0.f)
-#pragma unroll
+#pragma unroll 1
         for (int c4 = 0; c4 < 4; ++c4) {
+          uint32_t pk[16];
+          if ((cls_none >> c4) & 1u) {
+#pragma unroll
+            for (int k = 0; k < 16; ++k) pk[k] = 0u;
+            tmem_st16(ts + c4 * 16, pk);
+            continue;
+          }
           uint32_t v[32];
           tmem_ld32(ts + c4 * 32, v);
           tc_wait_ld();
-          uint32_t pk[16];
+          if (!((cls_mixed >> c4) & 1u)) {
 #pragma unroll
-          for (int k = 0; k < 16; ++k) {
-            float x0 = __uint_as_float(v[2 * k]), x1 = __uint_as_float(v[2 * k + 1]);
-            if (masked) {
-              x0 = (c4 * 32 + 2 * k) <= limit ? x0 : -INFINITY;
-              x1 = (c4 * 32 + 2 * k + 1) <= limit ? x1 : -INFINITY;
+            for (int k = 0; k < 16; ++k) {
+              float y0, y1;
+              unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(v[2 * k]), __uint_as_float(v[2 * k + 1])), scale2, nmref2),
+                           y0, y1);
+              const float p0 = fast_exp2(y0), p1 = fast_exp2(y1);
+              ls2[k & 3] = add_f32x2(ls2[k & 3], pack_f32x2(p0, p1));
+              pk[k] = pack16(p0, p1, p.is_bf16);
             }
-            float y0, y1;
-            unpack_f32x2(fma_f32x2(pack_f32x2(x0, x1), scale2, nmref2), y0, y1);
-            const float p0 = fast_exp2(y0), p1 = fast_exp2(y1);
-            ls2[k & 3] = add_f32x2(ls2[k & 3], pack_f32x2(p0, p1));
-            pk[k] = pack16(p0, p1, p.is_bf16);
+          } else {
+            const int lim4 = limit - 32 * c4;
+#pragma unroll
+            for (int k = 0; k < 16; ++k) {
+              const float x0 = 2 * k <= lim4 ? __uint_as_float(v[2 * k]) : -INFINITY;
+              const float x1 = 2 * k + 1 <= lim4 ? __uint_as_float(v[2 * k + 1]) : -INFINITY;
+              float y0, y1;
+              unpack_f32x2(fma_f32x2(pack_f32x2(x0, x1), scale2, nmref2), y0, y1);
+              const float p0 = fast_exp2(y0), p1 = fast_exp2(y1);
+              ls2[k & 3] = add_f32x2(ls2[k & 3], pack_f32x2(p0, p1));
+              pk[k] = pack16(p0, p1, p.is_bf16);
+            }
           }
           tmem_st16(ts + c4 * 16, pk);
         }
@@ -429,7 +468,7 @@ block_sparse_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
         mbar_arrive(p_ready);
         if (threadIdx.x == (s << 7)) XB_TRACE_EV(0x33, bc);
       }
-      row = nrow; n = nn; win = nwin;
+      it = nit; n = nn; win = nwin;
     }
   } else {
     // -------------------------------------------------------------------- epilogue (warps 8-11), both streams
@@ -466,18 +505,25 @@ block_sparse_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
       const float l = s_l[(s * 2 + (m & 1)) * 128 + r];
       const float inv = l > 0.f ? 1.f / l : 0.f;
       const uint32_t tmem_o = tmem_base + 256 + s * 128 + lane_bits;
+      // A thread owns one output row, but a store instruction should write whole cache lines: each 64-column
+      // half of the warp's 32 rows goes through a 4 KiB shared-memory buffer (16-byte chunks XOR-swizzled by
+      // row against bank conflicts) and leaves as 8 instructions of 4 rows x 128 contiguous bytes.
+      uint8_t* stg = stage_base + quad * (32 * 128);
+      const int q_row0 = it.qb * 128 + quad * 32;                     // first row of this warp
+      uint8_t* obase = static_cast<uint8_t*>(out) +
+                       2 * (static_cast<int64_t>(it.b) * p.osb + static_cast<int64_t>(it.h) * p.osh);
 #pragma unroll
-      for (int c4 = 0; c4 < 4; ++c4) {
-        uint32_t v[32];
-        tmem_ld32(tmem_o + c4 * 32, v);
-        tc_wait_ld();
-        if (c4 == 3) {
-          // every read of this O buffer is done: the stream's next item may accumulate into it
-          tc_fence_before();
-          mbar_arrive(bar(s, O_EMPTY));
-        }
-        if (store) {
-          uint4* dst = reinterpret_cast<uint4*>(orow + c4 * 64);
+      for (int half = 0; half < 2; ++half) {
+#pragma unroll
+        for (int c2 = 0; c2 < 2; ++c2) {
+          uint32_t v[32];
+          tmem_ld32(tmem_o + half * 64 + c2 * 32, v);
+          tc_wait_ld();
+          if (half == 1 && c2 == 1) {
+            // every read of this O buffer is done: the stream's next item may accumulate into it
+            tc_fence_before();
+            mbar_arrive(bar(s, O_EMPTY));
+          }
 #pragma unroll
           for (int q4 = 0; q4 < 4; ++q4) {
             uint4 wv;
@@ -485,9 +531,21 @@ block_sparse_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
             wv.y = pack16(__uint_as_float(v[q4 * 8 + 2]) * inv, __uint_as_float(v[q4 * 8 + 3]) * inv, p.is_bf16);
             wv.z = pack16(__uint_as_float(v[q4 * 8 + 4]) * inv, __uint_as_float(v[q4 * 8 + 5]) * inv, p.is_bf16);
             wv.w = pack16(__uint_as_float(v[q4 * 8 + 6]) * inv, __uint_as_float(v[q4 * 8 + 7]) * inv, p.is_bf16);
-            dst[q4] = wv;
+            const int chunk = c2 * 4 + q4;                            // 16-byte chunk within the 128-byte half row
+            *reinterpret_cast<uint4*>(stg + lane * 128 + ((chunk ^ (lane & 7)) << 4)) = wv;
           }
         }
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int rr = 4 * i + (lane >> 3);                         // row within the warp's 32
+          const int chunk = lane & 7;
+          const uint4 wv = *reinterpret_cast<const uint4*>(stg + rr * 128 + ((chunk ^ (rr & 7)) << 4));
+          const int q_pos_r = q_row0 + rr;
+          if (q_pos_r < p.q_len)
+            *reinterpret_cast<uint4*>(obase + 2 * static_cast<int64_t>(q_pos_r) * p.osl + half * 128 + chunk * 16) = wv;
+        }
+        __syncwarp();
       }
       if (threadIdx.x == 256) XB_TRACE_EV(0x44 + s, m);
     }

@@ -64,15 +64,27 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait.  `abort_flag` lives in shared memory and is shared by all roles of the CTA.
+// try_wait with a suspend-time hint: the thread sleeps in hardware (no issue slots burnt) until the phase
+// completes or roughly `hint_ns` nanoseconds pass.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  `abort_flag` lives in shared memory and is shared by all roles of the CTA.  Waiting threads
+// are suspended by the hardware in slices of at most 20 us, so co-resident warps keep their issue slots.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-#pragma unroll 1
-  for (int i = 0; i < 128; ++i)
-    if (mbar_try_wait(bar, parity)) return true;
+  if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
 #pragma unroll 1
   while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait_hint(bar, parity, 20000u)) return true;
     if (*abort_flag) return false;
     if (clock64() - t0 > kWaitCycleLimit) {
       *abort_flag = 1;
