@@ -289,6 +289,35 @@ def test_prefill_dense_threshold_one_matches_sdpa():
     assert err.max() < OUT_MAX_ABS and err.mean() < OUT_MEAN_ABS, (err.max(), err.mean())
 
 
+def test_host_pipeline_equals_device_call():
+    """Xattention_prefill_host (pinned host tensors, kv groups streamed over PCIe) gives the bits of the
+    device call."""
+    import xattn_b200
+    from xattn_b200 import synth
+    q, k, v, w = synth.make_inputs("llama3_8b_32k", seed=5, heads_limit=3, seq_len=4096)
+    ref = xattn_b200.Xattention_prefill(q.to(DEV), k.to(DEV), v.to(DEV), 8, threshold=0.9, chunk_size=2048)
+    for gps in (1, 2):
+        out = xattn_b200.Xattention_prefill_host(q.pin_memory(), k.pin_memory(), v.pin_memory(), 8, threshold=0.9,
+                                                 chunk_size=2048, groups_per_step=gps)
+        assert not out.is_cuda and out.shape == q.shape
+        assert torch.equal(out, ref.cpu())
+
+
+def test_head_shards_concatenate_to_the_full_result():
+    """Two ranks' head shards, computed one after the other on this GPU, equal the unsharded call."""
+    import xattn_b200
+    from xattn_b200 import synth
+    from xattn_b200.sharding import prefill_sharded
+    q, k, v, w = synth.make_inputs("llama3_8b_32k", seed=6, heads_limit=2, seq_len=4096)
+    dq, dk, dv = q.to(DEV), k.to(DEV), v.to(DEV)
+    thr = torch.linspace(0.6, 0.95, q.shape[1])
+    full = xattn_b200.Xattention_prefill(dq, dk, dv, 8, threshold=thr, chunk_size=2048)
+    for world in (2, 4):
+        parts = [prefill_sharded(dq, dk, dv, xattn_b200.Xattention_prefill, world, r, threshold=thr, stride=8,
+                                 chunk_size=2048) for r in range(world)]
+        assert torch.equal(torch.cat(parts, dim=1), full)
+
+
 def test_runs_are_bit_identical():
     """Same inputs, two runs: identical bits (no race between the roles of a CTA)."""
     import xattn_b200

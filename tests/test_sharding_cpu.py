@@ -1,0 +1,78 @@
+"""Head sharding across ranks, exercised as two gloo processes on the CPU: the shard plan covers every head
+once, and running the path per shard (the CPU oracle stands in for the GPU op here) then gathering gives
+exactly the unsharded result -- no collective is needed on the data path."""
+import os
+import sys
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_shard_plan_covers_all_heads_once():
+    from xattn_b200.sharding import all_shards
+    for hq, hkv in ((32, 8), (28, 4), (24, 24), (8, 8), (4, 1)):
+        for world in (1, 2, 3, 4, 8):
+            shards = all_shards(hq, hkv, world)
+            cover = []
+            rep = hq // hkv
+            for q0, q1, k0, k1 in shards:
+                cover += list(range(q0, q1))
+                for h in range(q0, q1):
+                    assert k0 <= h // rep < k1          # the kv head each local query head reads is local
+            assert cover == list(range(hq)), (hq, hkv, world, shards)
+            sizes = [s[1] - s[0] for s in shards]
+            if world <= hkv:
+                assert max(sizes) - min(sizes) <= rep   # whole groups, as even as possible
+
+
+def test_host_pipeline_group_slices():
+    from xattn_b200.host_pipeline import group_slices
+    for hq, hkv, gps in ((32, 8, 1), (32, 8, 3), (28, 4, 2), (24, 24, 5)):
+        sl = group_slices(hq, hkv, gps)
+        assert [h for s in sl for h in range(s[0], s[1])] == list(range(hq))
+        assert [h for s in sl for h in range(s[2], s[3])] == list(range(hkv))
+
+
+def _oracle_prefill(q, k, v, threshold, stride, chunk_size, causal):
+    from oracle import xattn_oracle as orc
+    rep = q.shape[1] // k.shape[1]
+    _, mask = orc.xattn_estimate_oracle(q.float(), k.float().repeat_interleave(rep, 1), 128, stride, 1.0, threshold,
+                                        chunk_size, causal)
+    return orc.block_sparse_attention_oracle(q, k, v, mask, causal)
+
+
+def _worker(rank, world, port, hq, hkv, ret):
+    for p in (ROOT, os.path.join(ROOT, "x-attention_b200")):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    import torch.distributed as dist
+    from xattn_b200.sharding import prefill_sharded
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.set_num_threads(2)
+    g = torch.Generator().manual_seed(123)             # same full tensors on every rank
+    L = 512
+    q = torch.randn(1, hq, L, 128, generator=g)
+    k = torch.randn(1, hkv, L, 128, generator=g)
+    v = torch.randn(1, hkv, L, 128, generator=g)
+    thr = torch.linspace(0.5, 0.95, hq)
+    full = prefill_sharded(q, k, v, _oracle_prefill, world, rank, threshold=thr, gather=True,
+                           stride=16, chunk_size=256, causal=True)
+    want = _oracle_prefill(q, k, v, thr, 16, 256, True)
+    ret[rank] = float((full - want).abs().max())
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("hq,hkv,world", [(8, 2, 2), (4, 1, 2)])
+def test_sharded_equals_unsharded_gloo(hq, hkv, world):
+    port = 29500 + (os.getpid() % 2000) + hq
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_worker, args=(world, port, hq, hkv, ret), nprocs=world, join=True)
+    assert len(ret) == world
+    assert all(err == 0.0 for err in ret.values()), dict(ret)

@@ -15,7 +15,8 @@
 //                        warps run the epilogue: per row, max over the tile's visible columns, exp2,
 //                        sums over groups of block/S columns.  Output per (row, key block): an
 //                        un-normalised partial sum, plus the max it was taken against per (row, tile).
-//   est_finalize_kernel  per query block: combine the tiles' maxima, normalise and add the block/S rows.
+//   est_rowstat_kernel   per row: combine the tiles' maxima and sums into the row's max and 1/sum
+//   est_blocksum_kernel  per (query block, key block): normalise and add the block/S rows.
 #include <math.h>
 
 #include "host_common.cuh"
@@ -111,7 +112,7 @@ template <int RBS>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 est_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const EstGeom g,
                 const int* __restrict__ tile_lo, const int* __restrict__ tile_prefix, float* __restrict__ partial,
-                float* __restrict__ mtile, const uint32_t idesc, int* status) {
+                float2* __restrict__ mtile, const uint32_t idesc, int* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
@@ -178,6 +179,8 @@ est_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     // ------------------------------------------------------------ MMA issuer (one thread)
     if (lane == 0) {
       uint32_t it = 0, local_tile = 0;
+      const uint64_t a_desc0 = smem_desc_sw128(smem_u32(smem), 16, 1024);
+      const uint64_t b_desc0 = smem_desc_sw128(smem_u32(smem) + kABytes, 16, 1024);
       for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, ++local_tile) {
         const uint32_t acc = local_tile & 1;
         const uint32_t acc_ph = (local_tile >> 1) & 1;
@@ -190,14 +193,12 @@ est_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           const uint32_t ph = (it / kStages) & 1;
           if (!mbar_wait(full0 + 8 * s, ph, abort_flag)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(smem + s * kStageBytes);
-          const uint32_t b_addr = a_addr + kABytes;
+          // descriptors differ from the stage-0 ones only in the start-address field (units of 16 bytes)
+          const uint64_t a_desc = a_desc0 + static_cast<uint64_t>(s * (kStageBytes >> 4));
+          const uint64_t b_desc = b_desc0 + static_cast<uint64_t>(s * (kStageBytes >> 4));
 #pragma unroll
-          for (int k4 = 0; k4 < kTileK / 16; ++k4) {
-            const uint64_t a_desc = smem_desc_sw128(a_addr + k4 * 32, 16, 1024);
-            const uint64_t b_desc = smem_desc_sw128(b_addr + k4 * 32, 16, 1024);
-            mma_ss(d_tmem, a_desc, b_desc, idesc, (ks > 0 || k4 > 0) ? 1u : 0u);
-          }
+          for (int k4 = 0; k4 < kTileK / 16; ++k4)
+            mma_ss(d_tmem, a_desc + k4 * 2, b_desc + k4 * 2, idesc, (ks > 0 || k4 > 0) ? 1u : 0u);
           mma_commit(empty0 + 8 * s);          // stage reusable once these MMAs have read it
         }
         if (!ok) break;
@@ -244,6 +245,7 @@ est_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const bool row_ok = i < g.rows_total;
       float* prow = partial + (static_cast<size_t>(bh) * g.rows_total + (row_ok ? i : 0)) * g.kb_total;
       const int kb0 = nt * kGroups;
+      float tile_sum = 0.f;
 #pragma unroll 1
       for (int c8 = 0; c8 < kTileN / 32; ++c8) {
         uint32_t v[32];
@@ -265,6 +267,8 @@ est_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           const float p = (c >= clo && c <= chi) ? fast_exp2(x) : 0.f;
           gs[k / RBS] += p;
         }
+#pragma unroll
+        for (int q = 0; q < 32 / RBS; ++q) tile_sum += gs[q];
         if (row_ok) {
 #pragma unroll
           for (int q = 0; q < 32 / RBS; ++q) {
@@ -273,7 +277,8 @@ est_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           }
         }
       }
-      if (row_ok) mtile[(static_cast<size_t>(bh) * g.rows_total + i) * g.n_ntiles + nt] = m_scaled;
+      if (row_ok)
+        mtile[(static_cast<size_t>(bh) * g.rows_total + i) * g.n_ntiles + nt] = make_float2(m_scaled, tile_sum);
     }
   }
 
@@ -293,59 +298,60 @@ est_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
 }
 
-// One block per (query block, head): normalise the partial sums.
-__global__ void __launch_bounds__(128)
-est_finalize_kernel(const EstGeom g, const int* __restrict__ tile_lo, const int* __restrict__ tile_prefix,
-                    const float* __restrict__ partial, const float* __restrict__ mtile, float* __restrict__ sums) {
-  __shared__ float row_m[32];
-  __shared__ float row_linv[32];
-  const int qb = blockIdx.x, bh = blockIdx.y;
+// Normalisation of the partial sums, as two streaming kernels.
+//   est_rowstat_kernel  one thread per reshaped row i:  m_i = max_t m_{i,t},
+//                       1/l_i with l_i = sum_t s_{i,t} 2^(m_{i,t} - m_i)      (m, s = per-tile max and sum)
+//   est_blocksum_kernel one thread per (query block, key block):
+//                       out[qb][kb] = sum_{i in qb} partial[i][kb] * 2^(m_{i,t(kb)} - m_i) / l_i
+__global__ void __launch_bounds__(256)
+est_rowstat_kernel(const EstGeom g, const int* __restrict__ tile_lo, const int* __restrict__ tile_prefix,
+                   const float2* __restrict__ mtile, float2* __restrict__ rowstat, int total_rows) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total_rows) return;
+  const int i = idx % g.rows_total;
+  const int mt = i / kTileM;
+  const int nlo = tile_lo[mt];
+  const int ncnt = tile_prefix[mt + 1] - tile_prefix[mt];
+  const float2* mrow = mtile + static_cast<size_t>(idx) * g.n_ntiles + nlo;
+  float m = -INFINITY, l = 0.f;
+  if (i < g.rows_valid) {
+    for (int t = 0; t < ncnt; ++t) m = fmaxf(m, mrow[t].x);
+    if (m > -INFINITY)
+      for (int t = 0; t < ncnt; ++t) {
+        const float2 ms = mrow[t];
+        if (ms.x > -INFINITY) l += ms.y * exp2f(ms.x - m);
+      }
+  }
+  rowstat[idx] = make_float2(m, l > 0.f ? 1.f / l : 0.f);
+}
+
+__global__ void __launch_bounds__(256)
+est_blocksum_kernel(const EstGeom g, const int* __restrict__ tile_lo, const int* __restrict__ tile_prefix,
+                    const float* __restrict__ partial, const float2* __restrict__ mtile,
+                    const float2* __restrict__ rowstat, float* __restrict__ sums) {
+  const int kb = blockIdx.x * blockDim.x + threadIdx.x;
+  const int qb = blockIdx.y, bh = blockIdx.z;
+  if (kb >= g.kb_total) return;
   const int i0 = qb * g.rbs;
   const int mt = i0 / kTileM;
   const int nlo = tile_lo[mt];
   const int ncnt = tile_prefix[mt + 1] - tile_prefix[mt];
   const int gpt = kTileN / g.rbs;                         // key blocks per tile
-  const int kb_lo = nlo * gpt;
-  int kb_hi = (nlo + ncnt) * gpt;                         // exclusive
-  if (kb_hi > g.kb_total) kb_hi = g.kb_total;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int row = warp; row < g.rbs; row += 4) {
-    const int i = i0 + row;
-    const float* mrow = mtile + (static_cast<size_t>(bh) * g.rows_total + i) * g.n_ntiles;
-    const float* prow = partial + (static_cast<size_t>(bh) * g.rows_total + i) * g.kb_total;
-    float m = -INFINITY;
-    if (i < g.rows_valid)
-      for (int t = lane; t < ncnt; t += 32) m = fmaxf(m, mrow[nlo + t]);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-    float l = 0.f;
-    if (i < g.rows_valid && m > -INFINITY)
-      for (int kb = kb_lo + lane; kb < kb_hi; kb += 32) {
-        const float mt_ = mrow[kb / gpt];
-        if (mt_ > -INFINITY) l += prow[kb] * exp2f(mt_ - m);
-      }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
-    if (lane == 0) {
-      row_m[row] = m;
-      row_linv[row] = l > 0.f ? 1.f / l : 0.f;
+  const int t = kb / gpt;
+  float acc = 0.f;
+  if (t >= nlo && t < nlo + ncnt) {
+    const size_t r0 = static_cast<size_t>(bh) * g.rows_total + i0;
+    int rows = g.rows_valid - i0;                         // rows past rows_valid contribute nothing
+    rows = rows > g.rbs ? g.rbs : rows;
+#pragma unroll 4
+    for (int row = 0; row < rows; ++row) {
+      const float2 st = rowstat[r0 + row];
+      const float mx = mtile[(r0 + row) * g.n_ntiles + t].x;
+      const float pv = partial[(r0 + row) * g.kb_total + kb];
+      if (st.y > 0.f && mx > -INFINITY) acc += pv * exp2f(mx - st.x) * st.y;
     }
   }
-  __syncthreads();
-  float* out = sums + (static_cast<size_t>(bh) * g.qb_total + qb) * g.kb_total;
-  for (int kb = threadIdx.x; kb < g.kb_total; kb += blockDim.x) {
-    float acc = 0.f;
-    if (kb >= kb_lo && kb < kb_hi) {
-      for (int row = 0; row < g.rbs; ++row) {
-        const float linv = row_linv[row];
-        if (linv == 0.f) continue;
-        const size_t ri = static_cast<size_t>(bh) * g.rows_total + i0 + row;
-        const float mt_ = mtile[ri * g.n_ntiles + kb / gpt];
-        if (mt_ > -INFINITY) acc += partial[ri * g.kb_total + kb] * exp2f(mt_ - row_m[row]) * linv;
-      }
-    }
-    out[kb] = acc;
-  }
+  sums[(static_cast<size_t>(bh) * g.qb_total + qb) * g.kb_total + kb] = acc;
 }
 
 // x = hi + mid + lo in bf16; rows widened to 6*D (see the header).
@@ -375,7 +381,7 @@ __global__ void split_f32_kernel(const float* __restrict__ x, int heads, int len
 
 // ------------------------------------------------------------------------------------ host side
 struct EstWorkspace {
-  size_t off_tile_lo, off_tile_prefix, off_mtile, off_partial, total;
+  size_t off_tile_lo, off_tile_prefix, off_rowstat, off_mtile, off_partial, total;
 };
 
 static int fill_geometry(int batch, int hq, int hkv, int q_len, int k_len, int head_dim, int stride, int block_size,
@@ -413,7 +419,8 @@ static EstWorkspace workspace_layout(const EstGeom& g) {
   w.off_tile_lo = o; o = up(o + sizeof(int) * g.n_mtiles);
   w.off_tile_prefix = o; o = up(o + sizeof(int) * (g.n_mtiles + 1));
   const size_t rows = static_cast<size_t>(g.batch) * g.hq * g.rows_total;
-  w.off_mtile = o; o = up(o + sizeof(float) * rows * g.n_ntiles);
+  w.off_rowstat = o; o = up(o + sizeof(float2) * rows);
+  w.off_mtile = o; o = up(o + sizeof(float2) * rows * g.n_ntiles);
   w.off_partial = o; o = up(o + sizeof(float) * rows * g.kb_total);
   w.total = o;
   return w;
@@ -446,7 +453,8 @@ int estimate_launch(const void* q, const void* k, int dtype, int batch, int hq, 
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   int* tile_lo = reinterpret_cast<int*>(ws + w.off_tile_lo);
   int* tile_prefix = reinterpret_cast<int*>(ws + w.off_tile_prefix);
-  float* mtile = reinterpret_cast<float*>(ws + w.off_mtile);
+  float2* mtile = reinterpret_cast<float2*>(ws + w.off_mtile);
+  float2* rowstat = reinterpret_cast<float2*>(ws + w.off_rowstat);
   float* partial = reinterpret_cast<float*>(ws + w.off_partial);
 
   // 5-D views [head_dim, S, len/S, heads, batch] whose second coordinate picks the token inside a stride group
@@ -486,8 +494,14 @@ int estimate_launch(const void* q, const void* k, int dtype, int batch, int hq, 
   }
   if (rc) return rc;
 
-  est_finalize_kernel<<<dim3(g.qb_total, batch * hq), 128, 0, stream>>>(g, tile_lo, tile_prefix, partial, mtile,
-                                                                        attn_sums);
+  const long long total_rows = static_cast<long long>(batch) * hq * g.rows_total;
+  if (total_rows > 0x7fffffffLL || batch * hq > 65535 || g.qb_total > 65535) return XATTN_B200_ERR_LIMIT;
+  est_rowstat_kernel<<<static_cast<int>((total_rows + 255) / 256), 256, 0, stream>>>(
+      g, tile_lo, tile_prefix, mtile, rowstat, static_cast<int>(total_rows));
+  if ((rc = launch_status())) return rc;
+  const int bt = g.kb_total >= 256 ? 256 : ((g.kb_total + 31) / 32) * 32;
+  est_blocksum_kernel<<<dim3((g.kb_total + bt - 1) / bt, g.qb_total, batch * hq), bt, 0, stream>>>(
+      g, tile_lo, tile_prefix, partial, mtile, rowstat, attn_sums);
   return launch_status();
 }
 

@@ -1,0 +1,107 @@
+"""Xattention_prefill for inputs that live in (pinned) host memory.
+
+Every (batch, kv-head group) of the path is independent, so the call is cut into kv-head groups and the
+three engines of the GPU work at the same time: while group g is computed, the q/k/v of group g+1 come
+in over PCIe and the output of group g-1 goes back (PCIe is full duplex).  Two device buffer sets rotate;
+all ordering is by CUDA events, the host thread does not block until the final wait.
+
+The reference has no counterpart (its callers hand over device tensors); this is the end-to-end path the
+benchmark times with host buffers.
+"""
+from __future__ import annotations
+
+from typing import Optional, Union
+
+import torch
+
+from . import ops
+
+_copy_streams = {}
+
+
+def _streams(device: torch.device):
+    key = device.index
+    s = _copy_streams.get(key)
+    if s is None:
+        s = (torch.cuda.Stream(device), torch.cuda.Stream(device))
+        _copy_streams[key] = s
+    return s
+
+
+def group_slices(hq: int, hkv: int, groups_per_step: int = 1):
+    """[(q_head_start, q_head_end, kv_head_start, kv_head_end)] covering all heads, kv groups kept whole."""
+    rep = hq // hkv
+    out = []
+    for g0 in range(0, hkv, groups_per_step):
+        g1 = min(hkv, g0 + groups_per_step)
+        out.append((g0 * rep, g1 * rep, g0, g1))
+    return out
+
+
+def Xattention_prefill_host(query_states: torch.Tensor, key_states: torch.Tensor, value_states: torch.Tensor,
+                            stride, norm=1, threshold: Union[float, torch.Tensor] = 0.8, block_size=128,
+                            causal=True, chunk_size=None, keep_sink=False, keep_recent=False,
+                            device: Optional[torch.device] = None, out: Optional[torch.Tensor] = None,
+                            groups_per_step: int = 1) -> torch.Tensor:
+    """Same computation as Xattention_prefill (xattn/src/Xattention.py:302-402) for host tensors.
+
+    query_states [1,Hq,L,D], key/value_states [1,Hkv,L,D] on the CPU (pin them: pageable memory makes the
+    copies synchronous).  Returns a pinned CPU tensor [1,Hq,L,D] (contiguous), or fills `out`.  The call
+    returns when the result is complete."""
+    assert block_size == 128
+    B, Hq, Lq, D = query_states.shape
+    assert B == 1
+    Hkv, Lk = key_states.shape[1], key_states.shape[2]
+    if query_states.is_cuda or key_states.is_cuda or value_states.is_cuda:
+        raise ValueError("Xattention_prefill_host takes host tensors; use Xattention_prefill for device tensors")
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    if chunk_size is None:
+        chunk_size = ops.default_chunk_size(Lk)
+    cdtype = torch.bfloat16 if query_states.dtype == torch.float32 else query_states.dtype
+    if out is None:
+        out = torch.empty(1, Hq, Lq, D, dtype=cdtype).pin_memory()
+    g = ops.geometry(Lq, Lk, chunk_size, stride, block_size)
+    slices = group_slices(Hq, Hkv, groups_per_step)
+    nq = slices[0][1] - slices[0][0]
+    nk = slices[0][3] - slices[0][2]
+    with torch.cuda.device(dev):
+        h2d, d2h = _streams(dev)
+        compute = torch.cuda.current_stream(dev)
+        bufs = []
+        for _ in range(2):
+            bufs.append(dict(
+                q=torch.empty(1, nq, Lq, D, dtype=query_states.dtype, device=dev),
+                k=torch.empty(1, nk, Lk, D, dtype=key_states.dtype, device=dev),
+                v=torch.empty(1, nk, Lk, D, dtype=value_states.dtype, device=dev),
+                o=torch.empty(1, nq, Lq, D, dtype=cdtype, device=dev),
+                loaded=torch.cuda.Event(), computed=torch.cuda.Event(), stored=torch.cuda.Event(), used=False))
+        h2d.wait_stream(compute)
+        for i, (q0, q1, k0, k1) in enumerate(slices):
+            b = bufs[i & 1]
+            hq_n, hk_n = q1 - q0, k1 - k0
+            with torch.cuda.stream(h2d):
+                if b["used"]:
+                    h2d.wait_event(b["computed"])          # inputs of step i-2 no longer needed
+                b["q"][:, :hq_n].copy_(query_states[:, q0:q1], non_blocking=True)
+                b["k"][:, :hk_n].copy_(key_states[:, k0:k1], non_blocking=True)
+                b["v"][:, :hk_n].copy_(value_states[:, k0:k1], non_blocking=True)
+                b["loaded"].record(h2d)
+            compute.wait_event(b["loaded"])
+            if b["used"]:
+                compute.wait_event(b["stored"])            # output buffer of step i-2 has left the device
+            thr = threshold[q0:q1] if isinstance(threshold, torch.Tensor) else threshold
+            qd, kd, vd = b["q"][:, :hq_n], b["k"][:, :hk_n], b["v"][:, :hk_n]
+            sums = ops.estimate_block_sums(qd, kd, stride, block_size, chunk_size, float(norm), bool(causal))
+            _, idx, cnt = ops.select_blocks(sums, g["bpc"], g["block_offset"], thr, bool(causal), True,
+                                            bool(keep_sink), bool(keep_recent), list_shape=(Lq, Lk), want_mask=False)
+            ops.block_sparse_attention(qd, kd, vd, idx, cnt, bool(causal), out=b["o"][:, :hq_n])
+            b["computed"].record(compute)
+            with torch.cuda.stream(d2h):
+                d2h.wait_event(b["computed"])
+                out[:, q0:q1].copy_(b["o"][:, :hq_n], non_blocking=True)
+                b["stored"].record(d2h)
+            b["used"] = True
+        compute.wait_stream(d2h)
+        compute.wait_stream(h2d)
+        compute.synchronize()
+    return out

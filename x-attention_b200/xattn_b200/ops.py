@@ -206,10 +206,12 @@ def mask_to_lists(mask: torch.Tensor, q_len: int, k_len: int, causal: bool):
 
 # ------------------------------------------------------------------------------ phase 3
 def block_sparse_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, block_idx: torch.Tensor,
-                           block_cnt: torch.Tensor, causal: bool = True, scale: Optional[float] = None
-                           ) -> torch.Tensor:
+                           block_cnt: torch.Tensor, causal: bool = True, scale: Optional[float] = None,
+                           out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """q [B,Hq,Lq,128], k/v [B,Hkv,Lk,128] (bf16/fp16; fp32 is computed in bf16) -> [B,Hq,Lq,128], returned
-    as a transposed view of [B,Lq,Hq,128] storage, like the reference's output (Xattention.py:392-394)."""
+    as a transposed view of [B,Lq,Hq,128] storage, like the reference's output (Xattention.py:392-394).
+    `out`, if given, is a [B,Hq,Lq,128] tensor of the compute dtype (any strides, unit stride on the last
+    dimension, 16-byte aligned rows) that receives the result instead."""
     _require_cuda(q, k, v, block_idx, block_cnt)
     lib = _lib.load()
     B, Hq, Lq, D = q.shape
@@ -223,14 +225,19 @@ def block_sparse_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, bl
         raise TypeError("q/k/v must share one of bf16, fp16, fp32")
     q, k, v = _aligned16(q), _aligned16(k), _aligned16(v)
     scale = 1.0 / math.sqrt(D) if scale is None else float(scale)
-    out = torch.empty(B, Lq, Hq, D, dtype=q.dtype, device=q.device)
+    if out is None:
+        out_view = torch.empty(B, Lq, Hq, D, dtype=q.dtype, device=q.device).transpose(1, 2)
+    else:
+        if tuple(out.shape) != (B, Hq, Lq, D) or out.dtype != q.dtype or out.stride(3) != 1 or not out.is_cuda:
+            raise ValueError("out must be a CUDA tensor [B,Hq,Lq,D] of the compute dtype with unit inner stride")
+        out_view = out
     lqb, lkb = (Lq + 127) // 128, (Lk + 127) // 128
     if tuple(block_idx.shape) != (B, Hq, lqb, lkb) or tuple(block_cnt.shape) != (B, Hq, lqb):
         raise ValueError("block lists have the wrong shape")
     _lib.check(lib.xattn_b200_block_sparse_attn(
         q.data_ptr(), k.data_ptr(), v.data_ptr(), _DT[q.dtype], B, Hq, Hkv, Lq, Lk, D,
         *_strides3(q), *_strides3(k), *_strides3(v), block_idx.contiguous().data_ptr(),
-        block_cnt.contiguous().data_ptr(), int(causal), scale, out.data_ptr(),
-        out.stride(0), out.stride(2), out.stride(1), _status(q.device).data_ptr(), _stream(q)), "block_sparse_attn")
-    out = out.transpose(1, 2)
-    return out.to(in_dtype) if in_dtype == torch.float32 else out
+        block_cnt.contiguous().data_ptr(), int(causal), scale, out_view.data_ptr(),
+        out_view.stride(0), out_view.stride(1), out_view.stride(2), _status(q.device).data_ptr(), _stream(q)),
+        "block_sparse_attn")
+    return out_view.to(in_dtype) if (in_dtype == torch.float32 and out is None) else out_view
