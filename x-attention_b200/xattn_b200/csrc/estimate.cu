@@ -25,7 +25,7 @@
 namespace xb {
 
 constexpr int kTileM = 128;
-constexpr int kTileN = 256;
+constexpr int kTileN = 256;                                  // widest column tile; EstGeom::tile_n is 256 or 128
 constexpr int kTileK = 64;                                   // elements per TMA box row = 128 bytes
 constexpr int kStages = 4;
 constexpr int kABytes = kTileM * kTileK * 2;                 // 16 KiB
@@ -44,6 +44,7 @@ struct EstGeom {
   int causal, left_blank;      // left_blank: columns left of the row's chunk are hidden (torch branch, un-padded K)
   int rbs, kb_total, qb_total;
   int n_mtiles, n_ntiles;
+  int tile_n;                  // columns per tile: 256, or 128 when no row sees more than 128 columns
   float scale_log2;
 };
 
@@ -79,8 +80,8 @@ __global__ void est_setup_kernel(EstGeom g, int* __restrict__ tile_lo, int* __re
       tile_lo[mt] = 0;
       s_cnt[mt] = 0;
     } else {
-      tile_lo[mt] = lo_min / kTileN;
-      s_cnt[mt] = hi_max / kTileN - lo_min / kTileN + 1;
+      tile_lo[mt] = lo_min / g.tile_n;
+      s_cnt[mt] = hi_max / g.tile_n - lo_min / g.tile_n + 1;
     }
   }
   __syncthreads();
@@ -169,9 +170,9 @@ est_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           const int t = ks / g.d_chunks;
           const int dc = ks - t * g.d_chunks;
           const uint32_t dstA = smem_u32(smem + s * kStageBytes);
-          mbar_expect_tx(full0 + 8 * s, kStageBytes);
+          mbar_expect_tx(full0 + 8 * s, kABytes + g.tile_n * kTileK * 2);
           tma_load_5d(dstA, &tmQ, full0 + 8 * s, dc * kTileK, g.S - 1 - t, mt * kTileM, h, b);
-          tma_load_5d(dstA + kABytes, &tmK, full0 + 8 * s, dc * kTileK, t, nt * kTileN, h / group, b);
+          tma_load_5d(dstA + kABytes, &tmK, full0 + 8 * s, dc * kTileK, t, nt * g.tile_n, h / group, b);
         }
       }
     }
@@ -209,7 +210,8 @@ est_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     // ------------------------------------------------------------ epilogue (4 warps, thread = tile row)
     const int quad = warp & 3;                  // TMEM lane quarter this warp may access
     const int r = quad * 32 + lane;
-    constexpr int kGroups = kTileN / RBS;       // key blocks per tile
+    const int kGroups = g.tile_n / RBS;         // key blocks per tile
+    const int n_chunks = g.tile_n / 32;
     uint32_t local_tile = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local_tile) {
       int bh, mt, nt;
@@ -219,9 +221,9 @@ est_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const int i = mt * kTileM + r;
       int lo, hi;
       row_bounds(g, i, lo, hi);
-      const int n0 = nt * kTileN;
+      const int n0 = nt * g.tile_n;
       const int clo = lo - n0 > 0 ? lo - n0 : 0;
-      const int chi = hi - n0 < kTileN - 1 ? hi - n0 : kTileN - 1;
+      const int chi = hi - n0 < g.tile_n - 1 ? hi - n0 : g.tile_n - 1;
       // warp-uniform: the tensor-memory loads below are warp-collective
       if (!__all_sync(0xffffffffu, mbar_wait(tfull0 + 8 * acc, acc_ph, abort_flag))) break;
       tc_fence_after();
@@ -229,7 +231,7 @@ est_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       // pass 1: row maximum over the visible columns of this tile
       float mx = -INFINITY;
 #pragma unroll 1
-      for (int c8 = 0; c8 < kTileN / 32; ++c8) {
+      for (int c8 = 0; c8 < n_chunks; ++c8) {
         uint32_t v[32];
         tmem_ld32(taddr + c8 * 32, v);
         tc_wait_ld();
@@ -247,11 +249,11 @@ est_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const int kb0 = nt * kGroups;
       float tile_sum = 0.f;
 #pragma unroll 1
-      for (int c8 = 0; c8 < kTileN / 32; ++c8) {
+      for (int c8 = 0; c8 < n_chunks; ++c8) {
         uint32_t v[32];
         tmem_ld32(taddr + c8 * 32, v);
         tc_wait_ld();
-        if (c8 == kTileN / 32 - 1) {
+        if (c8 == n_chunks - 1) {
           // all TMEM reads of this accumulator are done: hand it back to the MMA thread
           tc_fence_before();
           __syncwarp();
@@ -325,33 +327,45 @@ est_rowstat_kernel(const EstGeom g, const int* __restrict__ tile_lo, const int* 
   rowstat[idx] = make_float2(m, l > 0.f ? 1.f / l : 0.f);
 }
 
+// VEC consecutive key blocks per thread (4 when kb_total is a multiple of 4: one 16-byte store; they share a tile)
+template <int VEC>
 __global__ void __launch_bounds__(256)
 est_blocksum_kernel(const EstGeom g, const int* __restrict__ tile_lo, const int* __restrict__ tile_prefix,
                     const float* __restrict__ partial, const float2* __restrict__ mtile,
                     const float2* __restrict__ rowstat, float* __restrict__ sums) {
-  const int kb = blockIdx.x * blockDim.x + threadIdx.x;
+  const int kb = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
   const int qb = blockIdx.y, bh = blockIdx.z;
   if (kb >= g.kb_total) return;
   const int i0 = qb * g.rbs;
   const int mt = i0 / kTileM;
-  const int nlo = tile_lo[mt];
-  const int ncnt = tile_prefix[mt + 1] - tile_prefix[mt];
-  const int gpt = kTileN / g.rbs;                         // key blocks per tile
+  const int nlo = __ldg(tile_lo + mt);
+  const int ncnt = __ldg(tile_prefix + mt + 1) - __ldg(tile_prefix + mt);
+  const int gpt = g.tile_n / g.rbs;                       // key blocks per tile (a multiple of 4)
   const int t = kb / gpt;
-  float acc = 0.f;
+  float acc[VEC];
+#pragma unroll
+  for (int q = 0; q < VEC; ++q) acc[q] = 0.f;
   if (t >= nlo && t < nlo + ncnt) {
     const size_t r0 = static_cast<size_t>(bh) * g.rows_total + i0;
     int rows = g.rows_valid - i0;                         // rows past rows_valid contribute nothing
     rows = rows > g.rbs ? g.rbs : rows;
-#pragma unroll 4
+#pragma unroll 2
     for (int row = 0; row < rows; ++row) {
       const float2 st = rowstat[r0 + row];
       const float mx = mtile[(r0 + row) * g.n_ntiles + t].x;
-      const float pv = partial[(r0 + row) * g.kb_total + kb];
-      if (st.y > 0.f && mx > -INFINITY) acc += pv * exp2f(mx - st.x) * st.y;
+      const float f = (st.y > 0.f && mx > -INFINITY) ? exp2f(mx - st.x) * st.y : 0.f;
+      const float* pp = partial + (r0 + row) * g.kb_total + kb;
+      if (VEC == 4) {
+        const float4 pv = *reinterpret_cast<const float4*>(pp);
+        if (f != 0.f) { acc[0] += pv.x * f; acc[1 % VEC] += pv.y * f; acc[2 % VEC] += pv.z * f; acc[3 % VEC] += pv.w * f; }
+      } else {
+        if (f != 0.f) acc[0] += pp[0] * f;
+      }
     }
   }
-  sums[(static_cast<size_t>(bh) * g.qb_total + qb) * g.kb_total + kb] = acc;
+  float* out = sums + (static_cast<size_t>(bh) * g.qb_total + qb) * g.kb_total + kb;
+  if (VEC == 4) *reinterpret_cast<float4*>(out) = make_float4(acc[0], acc[1 % VEC], acc[2 % VEC], acc[3 % VEC]);
+  else out[0] = acc[0];
 }
 
 // x = hi + mid + lo in bf16; rows widened to 6*D (see the header).
@@ -407,7 +421,10 @@ static int fill_geometry(int batch, int hq, int hkv, int q_len, int k_len, int h
   g.rbs = block_size / stride;
   g.kb_total = lk / block_size; g.qb_total = lq / block_size;
   g.n_mtiles = (g.rows_total + kTileM - 1) / kTileM;
-  g.n_ntiles = (g.cols_total + kTileN - 1) / kTileN;
+  // narrow tiles when every row sees at most one 128-column span (torch branch with chunk_size <= 128*stride):
+  // a 256-wide tile would spend half of its MMA work on hidden columns
+  g.tile_n = (g.left_blank && g.rcs <= 128) ? 128 : kTileN;
+  g.n_ntiles = (g.cols_total + g.tile_n - 1) / g.tile_n;
   g.scale_log2 = scale * 1.4426950408889634f;
   return XATTN_B200_OK;
 }
@@ -470,14 +487,14 @@ int estimate_launch(const void* q, const void* k, int dtype, int batch, int hq, 
     const uint64_t dims[5] = {(uint64_t)head_dim, (uint64_t)stride, (uint64_t)(k_len / stride), (uint64_t)hkv,
                               (uint64_t)batch};
     const uint64_t str[4] = {(uint64_t)ksl * 2, (uint64_t)ksl * 2 * stride, (uint64_t)ksh * 2, (uint64_t)ksb * 2};
-    const uint32_t box[5] = {kTileK, 1, kTileN, 1, 1};
+    const uint32_t box[5] = {kTileK, 1, (uint32_t)g.tile_n, 1, 1};
     if ((rc = make_tmap_16bit(&tmK, k, 5, dims, str, box))) return rc;
   }
 
   est_setup_kernel<<<1, 256, sizeof(int) * g.n_mtiles, stream>>>(g, tile_lo, tile_prefix);
   if ((rc = launch_status())) return rc;
 
-  const uint32_t idesc = make_idesc_f16(kTileM, kTileN, dtype == XATTN_B200_BF16, false, false);
+  const uint32_t idesc = make_idesc_f16(kTileM, g.tile_n, dtype == XATTN_B200_BF16, false, false);
   const int grid = sm_count();
   auto launch = [&](auto kern) -> int {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem) != cudaSuccess)
@@ -499,9 +516,14 @@ int estimate_launch(const void* q, const void* k, int dtype, int batch, int hq, 
   est_rowstat_kernel<<<static_cast<int>((total_rows + 255) / 256), 256, 0, stream>>>(
       g, tile_lo, tile_prefix, mtile, rowstat, static_cast<int>(total_rows));
   if ((rc = launch_status())) return rc;
-  const int bt = g.kb_total >= 256 ? 256 : ((g.kb_total + 31) / 32) * 32;
-  est_blocksum_kernel<<<dim3((g.kb_total + bt - 1) / bt, g.qb_total, batch * hq), bt, 0, stream>>>(
-      g, tile_lo, tile_prefix, partial, mtile, rowstat, attn_sums);
+  const bool vec4 = g.kb_total % 4 == 0 && (reinterpret_cast<uintptr_t>(attn_sums) & 15) == 0;
+  const int per_row = vec4 ? g.kb_total / 4 : g.kb_total;
+  const int bt = per_row >= 256 ? 256 : ((per_row + 31) / 32) * 32;
+  const dim3 fgrid((per_row + bt - 1) / bt, g.qb_total, batch * hq);
+  if (vec4)
+    est_blocksum_kernel<4><<<fgrid, bt, 0, stream>>>(g, tile_lo, tile_prefix, partial, mtile, rowstat, attn_sums);
+  else
+    est_blocksum_kernel<1><<<fgrid, bt, 0, stream>>>(g, tile_lo, tile_prefix, partial, mtile, rowstat, attn_sums);
   return launch_status();
 }
 

@@ -34,7 +34,7 @@ struct SelParams {
   int list_q_blocks, list_k_blocks, list_q_len, list_k_len;
   int np2;            // k_blocks rounded up to a power of two (>= 32)
   int warps_per_cta;
-  int vals_bytes, keys_bytes, per_warp_bytes;
+  int vals_bytes, keys_bytes, per_warp_bytes;   // keys: one sort buffer per CTA, taken in turn by its warps
   int rows_total;
 };
 
@@ -54,16 +54,19 @@ __device__ __forceinline__ double warp_sum(double v) {
 
 __global__ void select_kernel(const float* __restrict__ sums, const SelParams p,
                               const float* __restrict__ thr_per_head, uint8_t* __restrict__ mask_out,
-                              int32_t* __restrict__ idx_out, int32_t* __restrict__ cnt_out) {
+                              int32_t* __restrict__ idx_out, int32_t* __restrict__ cnt_out, int* status) {
   extern __shared__ __align__(16) uint8_t sel_smem[];
+  __shared__ int sort_lock;
+  if (threadIdx.x == 0) sort_lock = 0;
+  __syncthreads();
   const int lane = threadIdx.x & 31;
   const int wib = threadIdx.x >> 5;
   const int w = blockIdx.x * p.warps_per_cta + wib;
   if (w >= p.rows_total) return;                         // whole warps leave; no block-wide barrier below
-  uint8_t* base_ptr = sel_smem + static_cast<size_t>(wib) * p.per_warp_bytes;
+  unsigned long long* keys = reinterpret_cast<unsigned long long*>(sel_smem);        // [np2], shared by the CTA
+  uint8_t* base_ptr = sel_smem + p.keys_bytes + static_cast<size_t>(wib) * p.per_warp_bytes;
   float* vals = reinterpret_cast<float*>(base_ptr);                                  // [N]  (-1 = removed)
-  unsigned long long* keys = reinterpret_cast<unsigned long long*>(base_ptr + p.vals_bytes);      // [np2]
-  uint8_t* mrow = base_ptr + p.vals_bytes + p.keys_bytes;                            // [N]
+  uint8_t* mrow = base_ptr + p.vals_bytes;                                           // [N]
 
   const int bh = w / p.q_blocks;
   const int R = w - bh * p.q_blocks;
@@ -129,6 +132,24 @@ __global__ void select_kernel(const float* __restrict__ sums, const SelParams p,
       ++i;
     }
     if (sort_rest) {
+      // the sort buffer is shared by the warps of the CTA (flat rows are the exception): take it in turn.
+      // The holder always releases it after a bounded amount of work; the spin itself is bounded too.
+      int got = 0;
+      if (lane == 0) {
+        for (long long spin = 0; spin < (1ll << 26); ++spin) {
+          if (atomicCAS(&sort_lock, 0, 1) == 0) { got = 1; break; }
+          __nanosleep(200);
+        }
+        __threadfence_block();
+      }
+      got = __shfl_sync(0xffffffffu, got, 0);
+      if (!got) {
+        if (lane == 0 && status) atomicExch(status, 101);
+        untaken = true;
+        sort_rest = false;
+      }
+    }
+    if (sort_rest) {
       // ranks i.. : sort what is left (descending score, ascending index), fp64 prefix, decide per rank
       for (int t = lane; t < p.np2; t += 32) {
         unsigned long long key = 0ull;
@@ -175,6 +196,11 @@ __global__ void select_kernel(const float* __restrict__ sums, const SelParams p,
         running += v;
       }
       if (__any_sync(0xffffffffu, ut)) untaken = true;
+      __syncwarp();
+      if (lane == 0) {
+        __threadfence_block();
+        atomicExch(&sort_lock, 0);
+      }
     }
   }
   __syncwarp();
@@ -231,7 +257,6 @@ int select_launch(const float* attn_sums, int batch, int heads, int q_blocks, in
                   int causal, int diagonal_cleanup, double threshold, const float* thr_per_head, int keep_sink, int keep_recent,
                   uint8_t* mask, int32_t* block_idx, int32_t* block_cnt, int list_q_blocks, int list_k_blocks,
                   int list_q_len, int list_k_len, int* status, cudaStream_t stream) {
-  (void)status;
   if (!attn_sums || batch < 1 || heads < 1 || q_blocks < 1 || k_blocks < 1 || bpc < 1 || block_offset < 0)
     return XATTN_B200_ERR_ARG;
   if (k_blocks > 8192) return XATTN_B200_ERR_LIMIT;
@@ -253,20 +278,20 @@ int select_launch(const float* attn_sums, int batch, int heads, int q_blocks, in
   p.np2 = np2;
   p.vals_bytes = (k_blocks * 4 + 15) & ~15;
   p.keys_bytes = np2 * 8;
-  p.per_warp_bytes = p.vals_bytes + p.keys_bytes + ((k_blocks + 15) & ~15);
-  int wpc = (56 * 1024) / p.per_warp_bytes;
+  p.per_warp_bytes = p.vals_bytes + ((k_blocks + 15) & ~15);
+  int wpc = (48 * 1024 - p.keys_bytes) / p.per_warp_bytes;
   wpc = wpc < 1 ? 1 : (wpc > 8 ? 8 : wpc);
   p.warps_per_cta = wpc;
   const long long rows = static_cast<long long>(batch) * heads * q_blocks;
   if (rows > 0x7fffffffLL) return XATTN_B200_ERR_LIMIT;
   p.rows_total = static_cast<int>(rows);
-  const size_t smem = static_cast<size_t>(wpc) * p.per_warp_bytes;
-  if (smem > 48 * 1024 &&
+  const size_t smem = static_cast<size_t>(p.keys_bytes) + static_cast<size_t>(wpc) * p.per_warp_bytes;
+  if (smem + 256 > 48 * 1024 &&
       cudaFuncSetAttribute(select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) !=
           cudaSuccess)
     return XATTN_B200_ERR_CUDA;
   const int grid = static_cast<int>((rows + wpc - 1) / wpc);
-  select_kernel<<<grid, wpc * 32, smem, stream>>>(attn_sums, p, thr_per_head, mask, block_idx, block_cnt);
+  select_kernel<<<grid, wpc * 32, smem, stream>>>(attn_sums, p, thr_per_head, mask, block_idx, block_cnt, status);
   return launch_status();
 }
 
