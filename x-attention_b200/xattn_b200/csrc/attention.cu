@@ -370,8 +370,23 @@ block_sparse_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
             else if (!all_vis) cls_mixed |= 1u << c4;
           }
         }
+        if (!masked) {
+          // two tensor-memory loads in flight per wait
 #pragma unroll 1
-        for (int c4 = 0; c4 < 4; ++c4) {
+          for (int c2 = 0; c2 < 2; ++c2) {
+            uint32_t v0[32], v1[32];
+            tmem_ld32(ts + c2 * 64, v0);
+            tmem_ld32(ts + c2 * 64 + 32, v1);
+            tc_wait_ld();
+#pragma unroll
+            for (int k = 0; k < 16; ++k) {
+              mx8[k & 7] = max3(mx8[k & 7], __uint_as_float(v0[2 * k]), __uint_as_float(v0[2 * k + 1]));
+              mx8[(k + 4) & 7] = max3(mx8[(k + 4) & 7], __uint_as_float(v1[2 * k]), __uint_as_float(v1[2 * k + 1]));
+            }
+          }
+        }
+#pragma unroll 1
+        for (int c4 = masked ? 0 : 4; c4 < 4; ++c4) {
           if ((cls_none >> c4) & 1u) continue;
           uint32_t v[32];
           tmem_ld32(ts + c4 * 32, v);
@@ -419,8 +434,35 @@ block_sparse_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
         unsigned long long ls2[4];
 #pragma unroll
         for (int q = 0; q < 4; ++q) ls2[q] = 0ull;     // (+0.f, +0.f)
+        if (!masked) {
+          // the load of the next 32 columns is in flight while the current ones are exponentiated
+          auto chunk = [&](const uint32_t (&v)[32], int c4) {
+            uint32_t pk[16];
+#pragma unroll
+            for (int k = 0; k < 16; ++k) {
+              float y0, y1;
+              unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(v[2 * k]), __uint_as_float(v[2 * k + 1])), scale2, nmref2),
+                           y0, y1);
+              const float p0 = fast_exp2(y0), p1 = fast_exp2(y1);
+              ls2[k & 3] = add_f32x2(ls2[k & 3], pack_f32x2(p0, p1));
+              pk[k] = pack16(p0, p1, p.is_bf16);
+            }
+            tmem_st16(ts + c4 * 16, pk);
+          };
+          uint32_t va[32], vb[32];
+          tmem_ld32(ts, va);
 #pragma unroll 1
-        for (int c4 = 0; c4 < 4; ++c4) {
+          for (int c2 = 0; c2 < 2; ++c2) {
+            tc_wait_ld();
+            tmem_ld32(ts + (2 * c2 + 1) * 32, vb);
+            chunk(va, 2 * c2);
+            tc_wait_ld();
+            if (c2 == 0) tmem_ld32(ts + 64, va);
+            chunk(vb, 2 * c2 + 1);
+          }
+        }
+#pragma unroll 1
+        for (int c4 = masked ? 0 : 4; c4 < 4; ++c4) {
           uint32_t pk[16];
           if ((cls_none >> c4) & 1u) {
 #pragma unroll
