@@ -270,6 +270,69 @@ def test_prefill_end_to_end_vs_oracle(name, L, heads):
     assert err.max() < OUT_MAX_ABS and err.mean() < OUT_MEAN_ABS, (err.max(), err.mean())
 
 
+def _check_workload(q, k, v, stride, threshold, chunk, causal, sample_rows=None):
+    """Mask parity with the oracle outside the margin, then output parity under the GPU's own mask."""
+    import xattn_b200
+    L = q.shape[2]
+    rep = q.shape[1] // k.shape[1]
+    dq, dk, dv = q.to(DEV), k.to(DEV), v.to(DEV)
+    sums, mask = xattn_b200.xattn_estimate(dq, dk, 128, stride, threshold=threshold, chunk_size=chunk, causal=causal)
+    osums, omask = orc.xattn_estimate_oracle(q.float(), k.float().repeat_interleave(rep, 1), 128, stride, 1.0,
+                                             threshold, chunk, causal)
+    assert torch.allclose(sums.float().cpu(), osums, rtol=2e-2, atol=2e-2)          # returned in bf16
+    ex = orc.margin_exempt(osums, L, L, 128, stride, chunk, threshold, causal)
+    d = (mask.cpu() != omask) & ~ex
+    assert not d.any(), d.nonzero()[:6].tolist()
+    assert int((mask.cpu() != omask).sum()) <= max(2, int(2e-3 * mask.numel()))
+    out = xattn_b200.Xattention_prefill(dq, dk, dv, stride, threshold=threshold, chunk_size=chunk, causal=causal)
+    qb = (L + 127) // 128
+    m = mask.cpu()[:, :, :qb, :qb]
+    if sample_rows is None:
+        ref = orc.block_sparse_attention_oracle(q, k, v, m, causal)
+        err = (out.float().cpu() - ref).abs()
+    else:
+        errs = []
+        for r in sample_rows:
+            r0, r1 = r * 128, min(L, (r + 1) * 128)
+            kk = k[:, :, :r1] if causal else k
+            vv = v[:, :, :r1] if causal else v
+            mm = m[:, :, r:r + 1, : (kk.shape[2] + 127) // 128]
+            ref = orc.block_sparse_attention_oracle(q[:, :, r0:r1], kk, vv, mm, causal)
+            errs.append((out[:, :, r0:r1].float().cpu() - ref).abs())
+        err = torch.cat(errs, dim=2)
+    assert err.max() < OUT_MAX_ABS and err.mean() < OUT_MEAN_ABS, (err.max(), err.mean())
+    return float(mask.float().mean())
+
+
+def test_llama_32k_full_length_one_kv_group():
+    """BASELINE configs[1] at its real length (32768, S=8, chunk 16384) on one kv group (4 query heads);
+    outputs checked on 12 query blocks spread over the sequence."""
+    from xattn_b200 import synth
+    q, k, v, w = synth.make_inputs("llama3_8b_32k", seed=1, heads_limit=1)
+    _check_workload(q, k, v, w.stride, w.threshold, w.chunk_size, True, sample_rows=[0, 1, 7, 31, 64, 100, 127, 128, 129, 200, 254, 255])
+
+
+def test_video_prefill_like_workload_padded_causal():
+    """Qwen2-VL-style sequence (text + frames + text), length not a multiple of the chunk (padded keys)."""
+    from xattn_b200 import synth
+    g = torch.Generator().manual_seed(4)
+    q, k, v = synth.video_like(g, 7, 1, text_pre=512, frames=22, frame_tokens=256, text_post=256)
+    q, k, v = q.bfloat16(), k.bfloat16(), v.bfloat16()
+    assert q.shape[2] == 6400
+    _check_workload(q, k, v, 16, 0.9, 4096, True)
+
+
+def test_dit_like_workload_non_causal_padded():
+    """HunyuanVideo-style full attention: non-causal, S=8, threshold 0.95, zero-padded keys take softmax mass
+    as in the reference."""
+    from xattn_b200 import synth
+    g = torch.Generator().manual_seed(6)
+    q, k, v = synth.dit_like(g, 3, frames=3, rows=20, cols=32, text_tokens=256)
+    q, k, v = q.bfloat16(), k.bfloat16(), v.bfloat16()
+    assert q.shape[2] == 2176
+    _check_workload(q, k, v, 8, 0.95, 2048, False)
+
+
 def test_prefill_dense_threshold_one_matches_sdpa():
     """threshold=1 keeps every causal block with mass: the op must equal dense causal attention
     (size-independent property, no oracle involved)."""
