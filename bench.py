@@ -314,9 +314,9 @@ def run_gpu_arm(args):
             higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16", data="synthetic",
             config=_config(w, chunk, n), clocks=clocks,
             e2e=dict(value=e2e_value, unit=UNIT, ms_per_step=ms_e2e, h2d_bytes_per_step=bi, d2h_bytes_per_step=bo),
-            gpu_launches=5 * args.steps,
-            kernels_per_step=["est_setup_kernel", "est_gemm_kernel", "est_finalize_kernel", "select_kernel",
-                              "block_sparse_attn_kernel"],
+            gpu_launches=7 * args.steps,
+            kernels_per_step=["est_setup_kernel", "est_gemm_kernel", "est_rowstat_kernel", "est_blocksum_kernel",
+                              "select_kernel", "block_sparse_attn_kernel<false>", "block_sparse_attn_kernel<true>"],
             phases_ms=dict(estimate=ph[0], select=ph[1], attend=ph[2]),
             block_density=density, roofline=roofline, cpu_baseline=cpu_baseline,
         )

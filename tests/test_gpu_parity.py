@@ -206,6 +206,42 @@ def test_block_sparse_attention_vs_oracle(causal, dtype, hq, hkv, lq, lk):
     assert err.max() < OUT_MAX_ABS and err.mean() < OUT_MEAN_ABS, (err.max(), err.mean())
 
 
+@pytest.mark.parametrize("causal,density,hq,hkv,L", [(True, 1.0, 2, 1, 4096), (False, 0.5, 2, 2, 3072), (True, 0.3, 4, 2, 5000)])
+def test_long_lists_take_the_half_block_path(causal, density, hq, hkv, L):
+    """Rows that list many blocks run through the half-block instantiation of the kernel (each 128-key block
+    as two 64-key halves); short lists (the other tests) through the full-block one.  Same oracle, same bars."""
+    from xattn_b200 import ops
+    g = torch.Generator().manual_seed(L + hq)
+    q = torch.randn(1, hq, L, 128, generator=g).bfloat16()
+    k = torch.randn(1, hkv, L, 128, generator=g).bfloat16()
+    v = torch.randn(1, hkv, L, 128, generator=g).bfloat16()
+    qb = (L + 127) // 128
+    mask = _random_block_mask(g, hq, qb, qb, causal, density)
+    idx, cnt = ops.mask_to_lists(mask.to(DEV), L, L, causal)
+    assert float(cnt.float().mean()) >= 5          # the kernel's switch-over point
+    out = ops.block_sparse_attention(q.to(DEV), k.to(DEV), v.to(DEV), idx, cnt, causal).float().cpu()
+    ref = orc.block_sparse_attention_oracle(q, k, v, mask, causal)
+    err = (out - ref).abs()
+    assert err.max() < OUT_MAX_ABS and err.mean() < OUT_MEAN_ABS, (err.max(), err.mean())
+
+
+def test_attention_rescale_path_long_list():
+    """Growing key norms force repeated lazy rescales of O, here on a list long enough for the half-block path."""
+    from xattn_b200 import ops
+    g = torch.Generator().manual_seed(78)
+    L = 2048
+    q = torch.randn(1, 1, L, 128, generator=g)
+    k = torch.randn(1, 1, L, 128, generator=g) * torch.linspace(6.0, 0.5, L)[None, None, :, None]   # early keys dominate
+    v = torch.randn(1, 1, L, 128, generator=g)
+    q, k, v = q.bfloat16(), k.bfloat16(), v.bfloat16()
+    mask = torch.tril(torch.ones(16, 16, dtype=torch.bool))[None, None].clone()
+    idx, cnt = ops.mask_to_lists(mask.to(DEV), L, L, True)
+    out = ops.block_sparse_attention(q.to(DEV), k.to(DEV), v.to(DEV), idx, cnt, True).float().cpu()
+    ref = orc.block_sparse_attention_oracle(q, k, v, mask, True)
+    err = (out - ref).abs()
+    assert torch.isfinite(out).all() and err.max() < 3e-2 and err.mean() < OUT_MEAN_ABS, (err.max(), err.mean())
+
+
 def test_attention_rescale_path_and_empty_rows():
     """Scores that grow block after block force the lazy rescale of O; rows with an empty list give zeros."""
     from xattn_b200 import ops

@@ -22,7 +22,11 @@
 //
 // Lists are walked from the last entry (the diagonal block when causal, which usually holds the row
 // maximum) to the first, so the running maximum settles at the first block and O is rarely rescaled.
-// TMEM columns: [0,128) S of stream 0, [128,256) S of stream 1, [256,384) O of stream 0, [384,512) O of stream 1.
+// Inside a stream every 128-key block is processed as two 64-key halves: S of half h goes to its own
+// 64-column TMEM buffer, so while the softmax warpgroup works on one half the tensor pipe computes the other
+// half's S (and the previous half's P.V).  K and V reach shared memory as four 16 KiB half-tiles per block.
+// TMEM columns: [0,128) S of stream 0 (two 64-column halves), [128,256) S of stream 1, [256,384) O of stream 0,
+// [384,512) O of stream 1.
 #include <math.h>
 
 #include "host_common.cuh"
@@ -33,10 +37,11 @@ namespace xb {
 constexpr int kAttnThreads = 512;
 constexpr int kTile16 = 128 * 128 * 2;     // one 128x128 16-bit tile = two 64-column TMA boxes
 constexpr int kHalf16 = kTile16 / 2;
+constexpr int kHalfTile = 64 * 128 * 2;    // 64 keys x 128 columns: [2 column halves][64 rows][64 columns]
 constexpr int kAttnSmemTiles = kTile16 * 6;                   // Q, K, V per stream
 constexpr int kSchedCap = 2048;                               // work items one CTA can schedule
 constexpr int kStageBytes = 4 * 32 * 128;                     // per epilogue warp: 32 rows x 64 16-bit columns
-constexpr int kAttnSmem = kAttnSmemTiles + 2 * 2 * 128 * 4 /*row sums*/ + 256 /*barriers*/ +
+constexpr int kAttnSmem = kAttnSmemTiles + 2 * 2 * 128 * 4 /*row sums*/ + 512 /*barriers*/ +
                           3 * kSchedCap * 2 /*schedule*/ + 16 + kStageBytes;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
@@ -118,17 +123,27 @@ struct Sched {
   int n_local, n_seq[2];
 };
 
+// kHalf selects how a stream walks a 128-key block: as two 64-key halves with their own S buffers (softmax of
+// one half overlaps the MMAs of the other: 62 % of the dense bf16 peak on long lists) or as one block (fewer
+// instructions and barriers: better when a row lists only a handful of blocks).  Both instantiations are
+// launched; each CTA sums its own block counts in the prologue and returns at once from the instantiation that
+// is not meant for its average list length, so the choice needs no host synchronisation.
+constexpr int kHalfModeMinBlocks = 5;    // average listed blocks per non-empty item from which halves pay off
+template <bool kHalf>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 block_sparse_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                         const __grid_constant__ CUtensorMap tmV, const AttnParams p,
+                         const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmKf,
+                         const __grid_constant__ CUtensorMap tmVf, const AttnParams p,
                          const int32_t* __restrict__ block_idx, const int32_t* __restrict__ block_cnt,
                          void* __restrict__ out, int* status) {
   extern __shared__ __align__(1024) uint8_t smem[];
   // tiles: [stream][Q, K, V]
   float* s_l = reinterpret_cast<float*>(smem + kAttnSmemTiles);          // [stream][2][128] final row sums
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kAttnSmemTiles + 2 * 2 * 128 * 4);
-  // per stream s: 10 barriers at bars[10*s + ...]
-  enum { Q_FULL = 0, Q_EMPTY, K_FULL, K_EMPTY, V_FULL, V_EMPTY, S_FULL, P_READY, O_FULL, O_EMPTY, NBAR };
+  // per stream s: NBAR barriers at bars[NBAR*s + ...].  H_* : the four half-tile slots of a block
+  // (0: keys 0-63 of K, 1: keys 64-127 of K, 2: keys 0-63 of V, 3: keys 64-127 of V); S_FULL/P_READY: per half
+  enum { Q_FULL = 0, Q_EMPTY, H_FULL, H_EMPTY = H_FULL + 4, S_FULL = H_EMPTY + 4, P_READY = S_FULL + 2,
+         O_FULL = P_READY + 2, O_EMPTY, PV_DONE, NBAR };
   const uint32_t bar0 = smem_u32(bars);
   auto bar = [&](int s, int which) -> uint32_t { return bar0 + 8u * (NBAR * s + which); };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * NBAR);
@@ -146,9 +161,48 @@ block_sparse_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
     return;
   }
 
+  // schedule table
+  uint16_t* sch_cnt = reinterpret_cast<uint16_t*>(smem + kAttnSmemTiles + 2 * 2 * 128 * 4 + 512);
+  uint16_t* sch_seq0 = sch_cnt + kSchedCap;
+  uint16_t* sch_seq1 = sch_seq0 + kSchedCap;
+  int* sch_total = reinterpret_cast<int*>(sch_seq1 + kSchedCap);
+  uint8_t* stage_base = reinterpret_cast<uint8_t*>(sch_total) + 16;     // 16-byte aligned (sch_total: 2 ints)
+  const int G = gridDim.x;
+  const int n_local = (p.total_items - static_cast<int>(blockIdx.x) + G - 1) / G;     // host guarantees <= kSchedCap
+  for (int i = threadIdx.x; i < n_local; i += kAttnThreads) {
+    const int c = __ldg(block_cnt + decode_item(p, blockIdx.x + i * G).row);
+    sch_cnt[i] = static_cast<uint16_t>(c > 65535 ? 65535 : c);
+  }
+  __syncthreads();
+  if (warp == 0) {
+    int running = 0, blocks = 0;
+    for (int base = 0; base < n_local; base += 32) {
+      const int i = base + lane;
+      const int c = i < n_local ? sch_cnt[i] : 0;
+      const bool ne = c > 0;
+      const unsigned bal = __ballot_sync(0xffffffffu, ne);
+      const int k = running + __popc(bal & ((1u << lane) - 1u));
+      if (ne) ((k & 1) ? sch_seq1 : sch_seq0)[k >> 1] = static_cast<uint16_t>(i);
+      running += __popc(bal);
+      blocks += c;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) blocks += __shfl_xor_sync(0xffffffffu, blocks, o);
+    if (lane == 0) {
+      sch_total[0] = running;
+      sch_total[1] = blocks;
+    }
+  }
+  __syncthreads();
+  {
+    // which instantiation serves this CTA: the other one returns here, before touching barriers or tensor memory
+    const bool want_half = sch_total[1] >= kHalfModeMinBlocks * sch_total[0];
+    if (want_half != kHalf) return;
+  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < 2; ++s)
-      for (int w = 0; w < NBAR; ++w) mbar_init(bar(s, w), (w == P_READY || w == O_EMPTY) ? 128 : 1);
+      for (int w = 0; w < NBAR; ++w)
+        mbar_init(bar(s, w), (w == P_READY || w == P_READY + 1 || w == O_EMPTY) ? 128 : 1);
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tmQ);
@@ -159,34 +213,9 @@ block_sparse_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
     tmem_alloc(smem_u32(tmem_slot), 512);
     tmem_relinquish();
   }
-  // schedule table
-  uint16_t* sch_cnt = reinterpret_cast<uint16_t*>(smem + kAttnSmemTiles + 2 * 2 * 128 * 4 + 256);
-  uint16_t* sch_seq0 = sch_cnt + kSchedCap;
-  uint16_t* sch_seq1 = sch_seq0 + kSchedCap;
-  int* sch_total = reinterpret_cast<int*>(sch_seq1 + kSchedCap);
-  uint8_t* stage_base = reinterpret_cast<uint8_t*>(sch_total) + 16;     // 16-byte aligned
-  const int G = gridDim.x;
-  const int n_local = (p.total_items - static_cast<int>(blockIdx.x) + G - 1) / G;     // host guarantees <= kSchedCap
-  for (int i = threadIdx.x; i < n_local; i += kAttnThreads) {
-    const int c = __ldg(block_cnt + decode_item(p, blockIdx.x + i * G).row);
-    sch_cnt[i] = static_cast<uint16_t>(c > 65535 ? 65535 : c);
-  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  if (warp == 0) {
-    int running = 0;
-    for (int base = 0; base < n_local; base += 32) {
-      const int i = base + lane;
-      const bool ne = i < n_local && sch_cnt[i] > 0;
-      const unsigned bal = __ballot_sync(0xffffffffu, ne);
-      const int k = running + __popc(bal & ((1u << lane) - 1u));
-      if (ne) ((k & 1) ? sch_seq1 : sch_seq0)[k >> 1] = static_cast<uint16_t>(i);
-      running += __popc(bal);
-    }
-    if (lane == 0) *sch_total = running;
-  }
-  __syncthreads();
   Sched sch;
   sch.cnt = sch_cnt;
   sch.seq[0] = sch_seq0;
@@ -198,7 +227,7 @@ block_sparse_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
   const int group = p.hq / p.hkv;
 
   if (warp >= 12) {
-    reg_dec<80>();
+    reg_dec<96>();
     const int s = (warp - 12) >> 1;                   // stream of this warp
     uint8_t* tiles = smem + s * 3 * kTile16;          // Q, K, V tiles of the stream
     if ((warp & 1) == 0) {
@@ -225,6 +254,9 @@ block_sparse_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
             XB_TRACE_EV(0x10, m);
             mbar_expect_tx(bar(s, Q_FULL), kTile16);
             tma_load_5d(smem_u32(tiles), &tmQ, bar(s, Q_FULL), 0, it.qb * 128, 0, it.h, it.b);
+            // the stream has one Q buffer, so the next item's Q can only be loaded when this item's last S is
+            // done: pull it into L2 now so that load does not wait on HBM
+            if (m + 1 < n_items) tma_prefetch_l2_5d(&tmQ, 0, nit.qb * 128, 0, nit.h, nit.b);
           } else {
             ok = 0;
           }
@@ -236,21 +268,34 @@ block_sparse_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
             w_next = list_window(p, block_idx, it.row, n, j + 32, lane);
           }
           const int k0 = __shfl_sync(0xffffffffu, w, j & 31) * 128;
+          if constexpr (kHalf) {
           if (lane == 0 && ok) {
-            if (mbar_wait(bar(s, K_EMPTY), (bc & 1) ^ 1, abort_flag)) {
+#pragma unroll
+            for (int slot = 0; slot < 4; ++slot) {
+              if (!mbar_wait(bar(s, H_EMPTY + slot), (bc & 1) ^ 1, abort_flag)) { ok = 0; break; }
+              XB_TRACE_EV(0x12 + (slot >> 1), bc * 2 + (slot & 1));
+              mbar_expect_tx(bar(s, H_FULL + slot), kHalfTile);
+              tma_load_5d(smem_u32(tiles + kTile16 + slot * kHalfTile), slot < 2 ? &tmK : &tmV, bar(s, H_FULL + slot), 0,
+                          k0 + (slot & 1) * 64, 0, hkv, it.b);
+            }
+          }
+          } else {
+          if (lane == 0 && ok) {
+            if (mbar_wait(bar(s, H_EMPTY), (bc & 1) ^ 1, abort_flag)) {
               XB_TRACE_EV(0x12, bc);
-              mbar_expect_tx(bar(s, K_FULL), kTile16);
-              tma_load_5d(smem_u32(tiles + kTile16), &tmK, bar(s, K_FULL), 0, k0, 0, hkv, it.b);
+              mbar_expect_tx(bar(s, H_FULL), kTile16);
+              tma_load_5d(smem_u32(tiles + kTile16), &tmKf, bar(s, H_FULL), 0, k0, 0, hkv, it.b);
             } else {
               ok = 0;
             }
-            if (ok && mbar_wait(bar(s, V_EMPTY), (bc & 1) ^ 1, abort_flag)) {
+            if (ok && mbar_wait(bar(s, H_EMPTY + 2), (bc & 1) ^ 1, abort_flag)) {
               XB_TRACE_EV(0x13, bc);
-              mbar_expect_tx(bar(s, V_FULL), kTile16);
-              tma_load_5d(smem_u32(tiles + 2 * kTile16), &tmV, bar(s, V_FULL), 0, k0, 0, hkv, it.b);
+              mbar_expect_tx(bar(s, H_FULL + 2), kTile16);
+              tma_load_5d(smem_u32(tiles + 2 * kTile16), &tmVf, bar(s, H_FULL + 2), 0, k0, 0, hkv, it.b);
             } else {
               ok = 0;
             }
+          }
           }
         }
         ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -258,8 +303,76 @@ block_sparse_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
       }
     } else if (lane == 0) {
       // ---------------------------------------------------------------- MMA issuer of stream s
-      const uint32_t idesc_qk = make_idesc_f16(128, 128, p.is_bf16 != 0, false, false);
       const uint32_t idesc_pv = make_idesc_f16(128, 128, p.is_bf16 != 0, false, true);
+      if constexpr (kHalf) {
+      const uint32_t qa = smem_u32(tiles), ha = smem_u32(tiles + kTile16);      // Q tile, four half-tile slots
+      const uint32_t sd = tmem_base + s * 128;          // S / P, half h at +64*h
+      const uint32_t od = tmem_base + 256 + s * 128;    // O
+      // operand descriptors never change: build them once.  Q: [2][128 rows][64]; K half: [2][64 keys][64];
+      // V half: [2][64 keys][64], MN-major (16 keys per step = 16 x 128 B rows, next 64 columns 8 KiB away)
+      uint64_t dq[8], dk[2][8], dv[2][4];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        dq[k] = smem_desc_sw128(qa + (k >> 2) * kHalf16 + (k & 3) * 32, 16, 1024);
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+          dk[h][k] = smem_desc_sw128(ha + h * kHalfTile + (k >> 2) * (kHalfTile / 2) + (k & 3) * 32, 16, 1024);
+      }
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          dv[h][k] = smem_desc_sw128(ha + (2 + h) * kHalfTile + k * 2048, kHalfTile / 2, 1024);
+      const uint32_t idesc_qk64 = make_idesc_f16(128, 64, p.is_bf16 != 0, false, false);
+      const int n_items = sch.n_seq[s];
+      bool ok = true;
+      // S of half h of block (m, j): needs Q (first block of an item) and K half h
+      auto issue_qk = [&](int m, int n, int j, uint32_t bc, int h) -> bool {
+        if (j == 0 && h == 0 && !mbar_wait(bar(s, Q_FULL), m & 1, abort_flag)) return false;
+        if (!mbar_wait(bar(s, H_FULL + h), bc & 1, abort_flag)) return false;
+        tc_fence_after();
+        XB_TRACE_EV(0x20 + h, bc);
+        mma_ss(sd + h * 64, dq[0], dk[h][0], idesc_qk64, 0u);
+#pragma unroll
+        for (int k = 1; k < 8; ++k) mma_ss(sd + h * 64, dq[k], dk[h][k], idesc_qk64, 1u);
+        mma_commit(bar(s, H_EMPTY + h));
+        mma_commit(bar(s, S_FULL + h));
+        if (h == 1 && j == n - 1) mma_commit(bar(s, Q_EMPTY));
+        return true;
+      };
+      // O += P V of half h: needs the softmax of that half and V half h
+      auto issue_pv = [&](int m, int n, int j, uint32_t bc, int h) -> bool {
+        if (j == 0 && h == 0 && !mbar_wait(bar(s, O_EMPTY), (m & 1) ^ 1, abort_flag)) return false;
+        if (!mbar_wait(bar(s, P_READY + h), bc & 1, abort_flag)) return false;
+        if (!mbar_wait(bar(s, H_FULL + 2 + h), bc & 1, abort_flag)) return false;
+        tc_fence_after();
+        XB_TRACE_EV(0x22 + h, bc);
+        mma_ts(od, sd + h * 64, dv[h][0], idesc_pv, (j > 0 || h > 0) ? 1u : 0u);
+#pragma unroll
+        for (int k = 1; k < 4; ++k) mma_ts(od, sd + h * 64 + k * 8, dv[h][k], idesc_pv, 1u);
+        mma_commit(bar(s, H_EMPTY + 2 + h));
+        mma_commit(bar(s, PV_DONE));
+        if (h == 1 && j == n - 1) mma_commit(bar(s, O_FULL));
+        return true;
+      };
+      // order inside the stream: ..., PV(b,0), QK(b+1,0), PV(b,1), QK(b+1,1), PV(b+1,0), ...
+      int m = 0, j = 0;
+      int n = n_items > 0 ? sch.cnt[sch.seq[s][0]] : 0;
+      uint32_t bc = 0;
+      if (n_items > 0) ok = issue_qk(m, n, j, bc, 0) && issue_qk(m, n, j, bc, 1);
+      while (ok && m < n_items) {
+        // the block after (m, j)
+        int m2 = m, j2 = j + 1, n2 = n;
+        if (j2 == n) { m2 = m + 1; j2 = 0; n2 = m2 < n_items ? sch.cnt[sch.seq[s][m2]] : 0; }
+        const bool has_next = m2 < n_items;
+        if (!issue_pv(m, n, j, bc, 0)) { ok = false; break; }
+        if (has_next && !issue_qk(m2, n2, j2, bc + 1, 0)) { ok = false; break; }
+        if (!issue_pv(m, n, j, bc, 1)) { ok = false; break; }
+        if (has_next && !issue_qk(m2, n2, j2, bc + 1, 1)) { ok = false; break; }
+        m = m2; j = j2; n = n2; ++bc;
+      }
+      } else {
+      const uint32_t idesc_qk = make_idesc_f16(128, 128, p.is_bf16 != 0, false, false);
       const uint32_t qa = smem_u32(tiles), ka = smem_u32(tiles + kTile16), va = smem_u32(tiles + 2 * kTile16);
       const uint32_t sd = tmem_base + s * 128;          // S / P
       const uint32_t od = tmem_base + 256 + s * 128;    // O
@@ -281,32 +394,181 @@ block_sparse_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
         for (int j = 0; j < n && ok; ++j, ++bc) {
           // S = Q K^T
           if (j == 0 && !mbar_wait(bar(s, Q_FULL), m & 1, abort_flag)) { ok = false; break; }
-          if (!mbar_wait(bar(s, K_FULL), bc & 1, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(bar(s, H_FULL), bc & 1, abort_flag)) { ok = false; break; }
           tc_fence_after();
           XB_TRACE_EV(0x20, bc);
           mma_ss(sd, dq[0], dk[0], idesc_qk, 0u);
 #pragma unroll
           for (int k = 1; k < 8; ++k) mma_ss(sd, dq[k], dk[k], idesc_qk, 1u);
-          mma_commit(bar(s, K_EMPTY));
+          mma_commit(bar(s, H_EMPTY));
           mma_commit(bar(s, S_FULL));
           if (j == n - 1) mma_commit(bar(s, Q_EMPTY));
           // O += P V
           if (!mbar_wait(bar(s, P_READY), bc & 1, abort_flag)) { ok = false; break; }
-          if (!mbar_wait(bar(s, V_FULL), bc & 1, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(bar(s, H_FULL + 2), bc & 1, abort_flag)) { ok = false; break; }
           if (j == 0 && !mbar_wait(bar(s, O_EMPTY), (m & 1) ^ 1, abort_flag)) { ok = false; break; }
           tc_fence_after();
           XB_TRACE_EV(0x22, bc);
           mma_ts(od, sd, dv[0], idesc_pv, j > 0 ? 1u : 0u);
 #pragma unroll
           for (int k = 1; k < 8; ++k) mma_ts(od, sd + k * 8, dv[k], idesc_pv, 1u);
-          mma_commit(bar(s, V_EMPTY));
+          mma_commit(bar(s, H_EMPTY + 2));
           if (j == n - 1) mma_commit(bar(s, O_FULL));
         }
+      }
       }
     }
   } else if (warp < 8) {
     // -------------------------------------------------------------------- softmax of stream (warp >> 2)
-    reg_inc<168>();
+    reg_inc<144>();
+    if constexpr (kHalf) {
+    const int s = warp >> 2;
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const uint32_t lane_bits = static_cast<uint32_t>(quad * 32) << 16;
+    const uint32_t ts0 = tmem_base + s * 128 + lane_bits;         // S / P of this stream, this row (half h at +64h)
+    const uint32_t tmem_o = tmem_base + 256 + s * 128 + lane_bits;
+    const int k_off = p.k_len - p.q_len;
+    const unsigned long long scale2 = pack_f32x2(p.scale_log2, p.scale_log2);
+    const int n_items = sch.n_seq[s];
+    uint32_t bc = 0;
+    bool ok = true;
+    Item it = decode_item(p, n_items > 0 ? blockIdx.x + sch.seq[s][0] * G : 0);
+    int n = n_items > 0 ? sch.cnt[sch.seq[s][0]] : 0;
+    int win = n_items > 0 ? list_window(p, block_idx, it.row, n, 0, lane) : 0;
+    for (int m = 0; m < n_items && ok; ++m) {
+      if (threadIdx.x == (s << 7)) XB_TRACE_EV(0x36, m);
+      // the stream's next item: fetch its first list window while this one is processed
+      Item nit = it;
+      int nn = 0, nwin = 0;
+      if (m + 1 < n_items) {
+        const int i2 = sch.seq[s][m + 1];
+        nit = decode_item(p, blockIdx.x + i2 * G);
+        nn = sch.cnt[i2];
+        nwin = list_window(p, block_idx, nit.row, nn, 0, lane);
+      }
+      const size_t row = it.row;
+      const int q_pos = it.qb * 128 + r;
+      int row_last = p.k_len - 1;                       // last key position this row may see
+      if (p.causal && q_pos + k_off < row_last) row_last = q_pos + k_off;
+      float m_used = -INFINITY, l = 0.f;
+      int w = win, w_next = list_window(p, block_idx, row, n, 32, lane);
+      for (int j = 0; j < n && ok; ++j, ++bc) {
+        if (j > 0 && (j & 31) == 0) {
+          w = w_next;
+          w_next = list_window(p, block_idx, row, n, j + 32, lane);
+        }
+        const int k0 = __shfl_sync(0xffffffffu, w, j & 31) * 128;
+#pragma unroll 1
+        for (int h = 0; h < 2; ++h) {
+          const int limit = row_last - k0 - 64 * h;       // columns c <= limit of this half are visible
+          const bool masked = __any_sync(0xffffffffu, limit < 63);
+          const uint32_t ts = ts0 + h * 64;
+          if (threadIdx.x == (s << 7)) XB_TRACE_EV(0x30, bc * 2 + h);
+          // waits are made warp-uniform: the tensor-memory loads/stores below are warp-collective
+          if (!__all_sync(0xffffffffu, mbar_wait(bar(s, S_FULL + h), bc & 1, abort_flag))) { ok = false; break; }
+          tc_fence_after();
+          if (threadIdx.x == (s << 7)) XB_TRACE_EV(0x31, bc * 2 + h);
+          // ---- pass 1: row maximum over the 64 columns, 8 chains of 3-input max, both loads in flight
+          float mx8[8];
+#pragma unroll
+          for (int q = 0; q < 8; ++q) mx8[q] = -INFINITY;
+          {
+            uint32_t v0[32], v1[32];
+            tmem_ld32(ts, v0);
+            tmem_ld32(ts + 32, v1);
+            tc_wait_ld();
+            if (!masked) {
+#pragma unroll
+              for (int k = 0; k < 16; ++k) {
+                mx8[k & 7] = max3(mx8[k & 7], __uint_as_float(v0[2 * k]), __uint_as_float(v0[2 * k + 1]));
+                mx8[(k + 4) & 7] = max3(mx8[(k + 4) & 7], __uint_as_float(v1[2 * k]), __uint_as_float(v1[2 * k + 1]));
+              }
+            } else {
+#pragma unroll
+              for (int k = 0; k < 16; ++k) {
+                mx8[k & 7] = max3(mx8[k & 7], 2 * k <= limit ? __uint_as_float(v0[2 * k]) : -INFINITY,
+                                  2 * k + 1 <= limit ? __uint_as_float(v0[2 * k + 1]) : -INFINITY);
+                mx8[(k + 4) & 7] = max3(mx8[(k + 4) & 7], 32 + 2 * k <= limit ? __uint_as_float(v1[2 * k]) : -INFINITY,
+                                        33 + 2 * k <= limit ? __uint_as_float(v1[2 * k + 1]) : -INFINITY);
+              }
+            }
+          }
+          const float mx = fmaxf(max3(mx8[0], mx8[1], mx8[2]), max3(max3(mx8[3], mx8[4], mx8[5]), mx8[6], mx8[7]));
+          const float m_new = fmaxf(m_used, mx * p.scale_log2);
+          const bool first = j == 0 && h == 0;
+          const bool need = m_new > m_used + kRescaleThreshold || first || (m_used == -INFINITY && m_new > -INFINITY);
+          if (__any_sync(0xffffffffu, need)) {
+            const float alpha = !need ? 1.f : (m_used == -INFINITY ? 0.f : fast_exp2(m_used - m_new));
+            if (!first) {
+              // O may be touched once every P.V issued so far for this stream has completed (the half before
+              // this one is the latest: its P.V cannot have been issued before this half's P is ready)
+              if (threadIdx.x == (s << 7)) XB_TRACE_EV(0x32, bc * 2 + h);
+              const uint32_t hq = bc * 2 + h;
+              if (!__all_sync(0xffffffffu, mbar_wait(bar(s, PV_DONE), (hq - 1) & 1, abort_flag))) { ok = false; break; }
+              tc_fence_after();
+#pragma unroll 1
+              for (int c4 = 0; c4 < 4; ++c4) {
+                uint32_t v[32];
+                tmem_ld32(tmem_o + c4 * 32, v);
+                tc_wait_ld();
+#pragma unroll
+                for (int k = 0; k < 32; ++k) v[k] = __float_as_uint(__uint_as_float(v[k]) * alpha);
+                tmem_st32(tmem_o + c4 * 32, v);
+              }
+            }
+            l *= alpha;
+            if (need) m_used = m_new;
+          }
+          const float m_ref = m_used == -INFINITY ? 0.f : m_used;
+          if (threadIdx.x == (s << 7)) XB_TRACE_EV(0x35, bc * 2 + h);
+          // ---- pass 2: exp2 of the two 32-column chunks; P chunk c (16 packed columns) overwrites S columns that
+          // were read already
+          const unsigned long long nmref2 = pack_f32x2(-m_ref, -m_ref);
+          unsigned long long ls2[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) ls2[q] = 0ull;     // (+0.f, +0.f)
+          auto chunk = [&](const uint32_t (&v)[32], int c) {
+            uint32_t pk[16];
+            const int lim = limit - 32 * c;
+#pragma unroll
+            for (int k = 0; k < 16; ++k) {
+              float x0 = __uint_as_float(v[2 * k]), x1 = __uint_as_float(v[2 * k + 1]);
+              if (masked) {
+                x0 = 2 * k <= lim ? x0 : -INFINITY;
+                x1 = 2 * k + 1 <= lim ? x1 : -INFINITY;
+              }
+              float y0, y1;
+              unpack_f32x2(fma_f32x2(pack_f32x2(x0, x1), scale2, nmref2), y0, y1);
+              const float p0 = fast_exp2(y0), p1 = fast_exp2(y1);
+              ls2[k & 3] = add_f32x2(ls2[k & 3], pack_f32x2(p0, p1));
+              pk[k] = pack16(p0, p1, p.is_bf16);
+            }
+            tmem_st16(ts + c * 16, pk);
+          };
+          {
+            uint32_t va[32], vb[32];
+            tmem_ld32(ts, va);
+            tmem_ld32(ts + 32, vb);
+            tc_wait_ld();
+            chunk(va, 0);
+            chunk(vb, 1);
+          }
+          {
+            float a0, a1;
+            unpack_f32x2(add_f32x2(add_f32x2(ls2[0], ls2[1]), add_f32x2(ls2[2], ls2[3])), a0, a1);
+            l += a0 + a1;
+          }
+          if (j == n - 1 && h == 1) s_l[(s * 2 + (m & 1)) * 128 + r] = l;   // for the epilogue of this item
+          tc_wait_st();
+          tc_fence_before();
+          mbar_arrive(bar(s, P_READY + h));
+          if (threadIdx.x == (s << 7)) XB_TRACE_EV(0x33, bc * 2 + h);
+        }
+      }
+      it = nit; n = nn; win = nwin;
+    }
+    } else {
     const int s = warp >> 2;
     const int quad = warp & 3;
     const int r = quad * 32 + lane;
@@ -512,9 +774,10 @@ block_sparse_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
       }
       it = nit; n = nn; win = nwin;
     }
+    }
   } else {
     // -------------------------------------------------------------------- epilogue (warps 8-11), both streams
-    reg_dec<96>();
+    reg_dec<128>();
     const int quad = warp & 3;
     const int r = quad * 32 + lane;
     const uint32_t lane_bits = static_cast<uint32_t>(quad * 32) << 16;
@@ -554,29 +817,36 @@ block_sparse_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
       const int q_row0 = it.qb * 128 + quad * 32;                     // first row of this warp
       uint8_t* obase = static_cast<uint8_t*>(out) +
                        2 * (static_cast<int64_t>(it.b) * p.osb + static_cast<int64_t>(it.h) * p.osh);
+      // O leaves tensor memory first (scaled and packed to 16 bit: 64 registers) so that the stream's next item
+      // can start accumulating while this one is still being stored
+      uint4 packed[16];
+#pragma unroll
+      for (int c2 = 0; c2 < 2; ++c2) {
+        uint32_t v0[32], v1[32];
+        tmem_ld32(tmem_o + c2 * 64, v0);
+        tmem_ld32(tmem_o + c2 * 64 + 32, v1);
+        tc_wait_ld();
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          packed[c2 * 8 + q4] = make_uint4(
+              pack16(__uint_as_float(v0[q4 * 8 + 0]) * inv, __uint_as_float(v0[q4 * 8 + 1]) * inv, p.is_bf16),
+              pack16(__uint_as_float(v0[q4 * 8 + 2]) * inv, __uint_as_float(v0[q4 * 8 + 3]) * inv, p.is_bf16),
+              pack16(__uint_as_float(v0[q4 * 8 + 4]) * inv, __uint_as_float(v0[q4 * 8 + 5]) * inv, p.is_bf16),
+              pack16(__uint_as_float(v0[q4 * 8 + 6]) * inv, __uint_as_float(v0[q4 * 8 + 7]) * inv, p.is_bf16));
+          packed[c2 * 8 + 4 + q4] = make_uint4(
+              pack16(__uint_as_float(v1[q4 * 8 + 0]) * inv, __uint_as_float(v1[q4 * 8 + 1]) * inv, p.is_bf16),
+              pack16(__uint_as_float(v1[q4 * 8 + 2]) * inv, __uint_as_float(v1[q4 * 8 + 3]) * inv, p.is_bf16),
+              pack16(__uint_as_float(v1[q4 * 8 + 4]) * inv, __uint_as_float(v1[q4 * 8 + 5]) * inv, p.is_bf16),
+              pack16(__uint_as_float(v1[q4 * 8 + 6]) * inv, __uint_as_float(v1[q4 * 8 + 7]) * inv, p.is_bf16));
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(bar(s, O_EMPTY));
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
 #pragma unroll
-        for (int c2 = 0; c2 < 2; ++c2) {
-          uint32_t v[32];
-          tmem_ld32(tmem_o + half * 64 + c2 * 32, v);
-          tc_wait_ld();
-          if (half == 1 && c2 == 1) {
-            // every read of this O buffer is done: the stream's next item may accumulate into it
-            tc_fence_before();
-            mbar_arrive(bar(s, O_EMPTY));
-          }
-#pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {
-            uint4 wv;
-            wv.x = pack16(__uint_as_float(v[q4 * 8 + 0]) * inv, __uint_as_float(v[q4 * 8 + 1]) * inv, p.is_bf16);
-            wv.y = pack16(__uint_as_float(v[q4 * 8 + 2]) * inv, __uint_as_float(v[q4 * 8 + 3]) * inv, p.is_bf16);
-            wv.z = pack16(__uint_as_float(v[q4 * 8 + 4]) * inv, __uint_as_float(v[q4 * 8 + 5]) * inv, p.is_bf16);
-            wv.w = pack16(__uint_as_float(v[q4 * 8 + 6]) * inv, __uint_as_float(v[q4 * 8 + 7]) * inv, p.is_bf16);
-            const int chunk = c2 * 4 + q4;                            // 16-byte chunk within the 128-byte half row
-            *reinterpret_cast<uint4*>(stg + lane * 128 + ((chunk ^ (lane & 7)) << 4)) = wv;
-          }
-        }
+        for (int chunk = 0; chunk < 8; ++chunk)
+          *reinterpret_cast<uint4*>(stg + lane * 128 + ((chunk ^ (lane & 7)) << 4)) = packed[half * 8 + chunk];
         __syncwarp();
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
@@ -608,15 +878,16 @@ block_sparse_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
   }
 }
 
-// [64 columns, rows, 2 column halves, heads, batch]: one box {64, 128, 2, 1, 1} brings a whole 128x128 tile
-// with a single TMA instruction, laid out as two 64-column swizzled halves one after the other.
+// [64 columns, rows, 2 column halves, heads, batch]: one box {64, rows, 2, 1, 1} brings `rows` x 128 columns
+// with a single TMA instruction, laid out as two 64-column swizzled halves one after the other (Q: 128 rows,
+// K/V: 64-key half tiles).
 static int make_qkv_map(CUtensorMap* m, const void* base, int len, int heads, int batch, int64_t sb, int64_t sh,
-                        int64_t sl) {
+                        int64_t sl, uint32_t box_rows) {
   const uint64_t dims[5] = {64, (uint64_t)len, 2, (uint64_t)heads, (uint64_t)batch};
   // a dimension of extent 1 never moves: give it a harmless valid stride
   const uint64_t s_h = heads > 1 ? (uint64_t)sh * 2 : 256, s_b = batch > 1 ? (uint64_t)sb * 2 : 256;
   const uint64_t str[4] = {(uint64_t)sl * 2, 128, s_h, s_b};
-  const uint32_t box[5] = {64, 128, 2, 1, 1};
+  const uint32_t box[5] = {64, box_rows, 2, 1, 1};
   return make_tmap_16bit(m, base, 5, dims, str, box);
 }
 
@@ -634,18 +905,22 @@ int block_sparse_attn_launch(const void* q, const void* k, const void* v, int dt
   if (!(scale > 0.f)) return XATTN_B200_ERR_ARG;
   int rc;
   if ((rc = check_sm100())) return rc;
-  CUtensorMap tmQ, tmK, tmV;
-  if ((rc = make_qkv_map(&tmQ, q, q_len, hq, batch, qsb, qsh, qsl))) return rc;
-  if ((rc = make_qkv_map(&tmK, k, k_len, hkv, batch, ksb, ksh, ksl))) return rc;
-  if ((rc = make_qkv_map(&tmV, v, k_len, hkv, batch, vsb, vsh, vsl))) return rc;
+  CUtensorMap tmQ, tmK, tmV, tmKf, tmVf;   // K/V as 64-key half tiles and as full 128-key tiles
+  if ((rc = make_qkv_map(&tmQ, q, q_len, hq, batch, qsb, qsh, qsl, 128))) return rc;
+  if ((rc = make_qkv_map(&tmK, k, k_len, hkv, batch, ksb, ksh, ksl, 64))) return rc;
+  if ((rc = make_qkv_map(&tmV, v, k_len, hkv, batch, vsb, vsh, vsl, 64))) return rc;
+  if ((rc = make_qkv_map(&tmKf, k, k_len, hkv, batch, ksb, ksh, ksl, 128))) return rc;
+  if ((rc = make_qkv_map(&tmVf, v, k_len, hkv, batch, vsb, vsh, vsl, 128))) return rc;
   AttnParams p;
   p.batch = batch; p.hq = hq; p.hkv = hkv; p.q_len = q_len; p.k_len = k_len;
   p.q_blocks = (q_len + 127) / 128; p.list_k_blocks = (k_len + 127) / 128;
   p.causal = causal ? 1 : 0; p.is_bf16 = dtype == XATTN_B200_BF16 ? 1 : 0;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.osb = osb; p.osh = osh; p.osl = osl;
-  if (cudaFuncSetAttribute(block_sparse_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem) !=
-      cudaSuccess)
+  if (cudaFuncSetAttribute(block_sparse_attn_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem) !=
+          cudaSuccess ||
+      cudaFuncSetAttribute(block_sparse_attn_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem) !=
+          cudaSuccess)
     return XATTN_B200_ERR_CUDA;
   const long long items = static_cast<long long>(batch) * hq * p.q_blocks;
   if (items > 0x7fffffffLL) return XATTN_B200_ERR_LIMIT;
@@ -653,8 +928,12 @@ int block_sparse_attn_launch(const void* q, const void* k, const void* v, int dt
   const int sms = sm_count();
   const int grid = items < sms ? static_cast<int>(items) : sms;
   if ((items + grid - 1) / grid > kSchedCap || p.list_k_blocks > 65535) return XATTN_B200_ERR_LIMIT;
-  block_sparse_attn_kernel<<<grid, kAttnThreads, kAttnSmem, stream>>>(tmQ, tmK, tmV, p, block_idx, block_cnt, out,
-                                                                      status);
+  // both instantiations; every CTA does its work in exactly one of them (see kHalfModeMinBlocks)
+  block_sparse_attn_kernel<false><<<grid, kAttnThreads, kAttnSmem, stream>>>(tmQ, tmK, tmV, tmKf, tmVf, p, block_idx,
+                                                                             block_cnt, out, status);
+  if ((rc = launch_status())) return rc;
+  block_sparse_attn_kernel<true><<<grid, kAttnThreads, kAttnSmem, stream>>>(tmQ, tmK, tmV, tmKf, tmVf, p, block_idx,
+                                                                            block_cnt, out, status);
   return launch_status();
 }
 
