@@ -284,6 +284,29 @@ def run_gpu_arm(args):
                     unit="TFLOP/s", frac=att_tflops / peaks["bf16"], traffic=None, peak_source=peaks["source"],
                     executed_flops_per_launch=f_att, selected_blocks=n_sel)
 
+    # the same attention kernel on a dense causal mask (long block lists): what the inner loop sustains when the
+    # per-item prologue/epilogue no longer dominates.  Rank 0 only, a few launches.
+    dense = None
+    if rank == 0:
+        Ld, Hd = 16384, 16
+        gd = torch.Generator().manual_seed(1)
+        qd_, kd_, vd_ = (torch.randn(1, Hd, Ld, 128, generator=gd).to(torch.bfloat16).to(device) for _ in range(3))
+        md = torch.tril(torch.ones(Ld // 128, Ld // 128, dtype=torch.bool, device=device))[None, None].expand(1, Hd, -1, -1)
+        idx_d, cnt_d = ops.mask_to_lists(md.contiguous(), Ld, Ld, True)
+        for _ in range(3):
+            ops.block_sparse_attention(qd_, kd_, vd_, idx_d, cnt_d, True)
+        d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        d0.record()
+        for _ in range(10):
+            ops.block_sparse_attention(qd_, kd_, vd_, idx_d, cnt_d, True)
+        d1.record()
+        torch.cuda.synchronize(device)
+        nb = int(cnt_d.sum())
+        tf = 4.0 * 128 * 128 * 128 * nb / (d0.elapsed_time(d1) / 10 * 1e-3) / 1e12
+        dense = dict(workload=f"dense causal mask, {Hd} heads x {Ld} tokens, {nb} blocks", achieved=tf,
+                     unit="TFLOP/s", peak=peaks["bf16"], frac=tf / peaks["bf16"])
+        del qd_, kd_, vd_, idx_d, cnt_d, md
+
     agg_flops = sum_over_ranks(effective_flops(w), dist, device)
     value = agg_flops / (ms * 1e-3) / 1e12
     e2e_value = agg_flops / (ms_e2e * 1e-3) / 1e12
@@ -318,7 +341,7 @@ def run_gpu_arm(args):
             kernels_per_step=["est_setup_kernel", "est_gemm_kernel", "est_rowstat_kernel", "est_blocksum_kernel",
                               "select_kernel", "block_sparse_attn_kernel<false>", "block_sparse_attn_kernel<true>"],
             phases_ms=dict(estimate=ph[0], select=ph[1], attend=ph[2]),
-            block_density=density, roofline=roofline, cpu_baseline=cpu_baseline,
+            block_density=density, roofline=roofline, attention_dense_mask=dense, cpu_baseline=cpu_baseline,
         )
         print(json.dumps(line), flush=True)
     if dist is not None:

@@ -417,6 +417,44 @@ def test_head_shards_concatenate_to_the_full_result():
         assert torch.equal(torch.cat(parts, dim=1), full)
 
 
+def test_query_chunk_shards_equal_the_full_call():
+    """Causal prefill cut into query chunks (as dealt to ranks for very long sequences), each computed
+    against the keys up to its own end, reproduces the single call bit for bit."""
+    import xattn_b200
+    from xattn_b200 import synth
+    from xattn_b200.sharding import prefill_query_chunk_sharded
+    q, k, v, w = synth.make_inputs("llama3_8b_128k", seed=9, heads_limit=1, seq_len=8192)
+    dq, dk, dv = q.to(DEV), k.to(DEV), v.to(DEV)
+    full = xattn_b200.Xattention_prefill(dq, dk, dv, 16, threshold=0.9, chunk_size=2048)
+    for world in (2, 4):
+        for r in range(world):
+            parts = prefill_query_chunk_sharded(dq, dk, dv, xattn_b200.Xattention_prefill, world, r, 2048,
+                                                threshold=0.9, stride=16)
+            for c, o in parts.items():
+                assert torch.equal(o, full[:, :, c * 2048:(c + 1) * 2048]), (world, r, c)
+
+
+def test_prefill_against_a_longer_key_cache():
+    """q shorter than k (chunked prefill against a cache): masks vs the oracle, outputs vs the oracle's
+    attention under the GPU mask, queries aligned to the end of the keys."""
+    import xattn_b200
+    from xattn_b200 import synth
+    g = torch.Generator().manual_seed(12)
+    Lq, Lk = 2048, 6144
+    q, k, v = synth.llama_like(g, 4, 2, Lk)
+    q = q[:, :, Lk - Lq:].contiguous().bfloat16()
+    k, v = k.bfloat16(), v.bfloat16()
+    sums, mask = xattn_b200.xattn_estimate(q.to(DEV), k.to(DEV), 128, 16, threshold=0.9, chunk_size=2048, causal=True)
+    osums, omask = orc.xattn_estimate_oracle(q.float(), k.float().repeat_interleave(2, 1), 128, 16, 1.0, 0.9, 2048, True)
+    ex = orc.margin_exempt(osums, Lq, Lk, 128, 16, 2048, 0.9, True)
+    d = (mask.cpu() != omask) & ~ex
+    assert not d.any(), d.nonzero()[:6].tolist()
+    out = xattn_b200.Xattention_prefill(q.to(DEV), k.to(DEV), v.to(DEV), 16, threshold=0.9, chunk_size=2048, causal=True)
+    ref = orc.block_sparse_attention_oracle(q, k, v, mask.cpu()[:, :, : Lq // 128, : Lk // 128], True)
+    err = (out.float().cpu() - ref).abs()
+    assert err.max() < OUT_MAX_ABS and err.mean() < OUT_MEAN_ABS, (err.max(), err.mean())
+
+
 def test_runs_are_bit_identical():
     """Same inputs, two runs: identical bits (no race between the roles of a CTA)."""
     import xattn_b200

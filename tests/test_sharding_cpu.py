@@ -36,6 +36,16 @@ def test_host_pipeline_group_slices():
         assert [h for s in sl for h in range(s[2], s[3])] == list(range(hkv))
 
 
+def test_query_chunk_plan_is_balanced_and_complete():
+    from xattn_b200.sharding import shard_query_chunks
+    for n, world in ((128, 8), (64, 4), (7, 2), (5, 8)):
+        owned = [shard_query_chunks(n, world, r) for r in range(world)]
+        assert sorted(c for o in owned for c in o) == list(range(n))
+        work = [sum(c + 1 for c in o) for o in owned]          # chunk c costs ~ c+1 key chunks
+        if n % (2 * world) == 0:
+            assert max(work) == min(work)
+
+
 def _oracle_prefill(q, k, v, threshold, stride, chunk_size, causal):
     from oracle import xattn_oracle as orc
     rep = q.shape[1] // k.shape[1]
@@ -66,6 +76,46 @@ def _worker(rank, world, port, hq, hkv, ret):
     ret[rank] = float((full - want).abs().max())
     dist.barrier()
     dist.destroy_process_group()
+
+
+def _worker_qchunks(rank, world, port, ret):
+    for p in (ROOT, os.path.join(ROOT, "x-attention_b200")):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    import torch.distributed as dist
+    from xattn_b200.sharding import prefill_query_chunk_sharded
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.set_num_threads(2)
+    g = torch.Generator().manual_seed(321)
+    L, chunk = 1024, 256
+    q = torch.randn(1, 2, L, 128, generator=g)             # every rank has its queries
+    k = torch.randn(1, 2, L, 128, generator=g)
+    v = torch.randn(1, 2, L, 128, generator=g)
+    if rank != 0:                                          # K/V only exist on rank 0 until the broadcast
+        k, v = torch.zeros_like(k), torch.zeros_like(v)
+    parts = prefill_query_chunk_sharded(q, k, v, _oracle_prefill, world, rank, chunk, threshold=0.9,
+                                        broadcast_kv_from=0, stride=16)
+    g2 = torch.Generator().manual_seed(321)
+    qf = torch.randn(1, 2, L, 128, generator=g2); kf = torch.randn(1, 2, L, 128, generator=g2); vf = torch.randn(1, 2, L, 128, generator=g2)
+    want = _oracle_prefill(qf, kf, vf, 0.9, 16, chunk, True)
+    err = 0.0
+    for c, o in parts.items():
+        err = max(err, float((o - want[:, :, c * chunk:(c + 1) * chunk]).abs().max()))
+    ret[rank] = (sorted(parts), err)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_query_chunk_sharding_with_kv_broadcast_gloo():
+    port = 31500 + (os.getpid() % 2000)
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_worker_qchunks, args=(2, port, ret), nprocs=2, join=True)
+    chunks = sorted(c for r in ret.values() for c in r[0])
+    assert chunks == [0, 1, 2, 3]
+    assert all(r[1] < 1e-5 for r in ret.values()), dict(ret)
 
 
 @pytest.mark.parametrize("hq,hkv,world", [(8, 2, 2), (4, 1, 2)])

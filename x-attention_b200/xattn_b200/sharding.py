@@ -75,3 +75,46 @@ def prefill_sharded(query_states: torch.Tensor, key_states: torch.Tensor, value_
     parts = [torch.empty_like(pad) for _ in range(world_size)]
     dist.all_gather(parts, pad.contiguous(), group=group)
     return torch.cat([p[:, : s[1] - s[0]] for p, s in zip(parts, shards)], dim=1)
+
+
+# ----------------------------------------------------------------------------------------------------------
+# Query-chunk sharding for sequences whose heads alone do not give enough parallelism (or whose K/V must be
+# replicated anyway): causal prefill only.
+# ----------------------------------------------------------------------------------------------------------
+def shard_query_chunks(n_chunks: int, world_size: int, rank: int) -> List[int]:
+    """Chunk indices owned by `rank`, dealt zig-zag (0,1,..,W-1,W-1,..,1,0,0,1,..) so that the causal work
+    (chunk c attends to c+1 chunks of keys) is balanced across ranks."""
+    out = []
+    for c in range(n_chunks):
+        lap, pos = divmod(c, world_size)
+        owner = pos if lap % 2 == 0 else world_size - 1 - pos
+        if owner == rank:
+            out.append(c)
+    return out
+
+
+def prefill_query_chunk_sharded(query_states: torch.Tensor, key_states: torch.Tensor, value_states: torch.Tensor,
+                                prefill_fn: Callable[..., torch.Tensor], world_size: int, rank: int, chunk_size: int,
+                                threshold=0.8, broadcast_kv_from: Optional[int] = None, group=None, **kwargs):
+    """Causal prefill with the QUERY axis cut into estimate chunks that are dealt to the ranks; every rank
+    needs all of K and V (one collective: `broadcast_kv_from` = source rank broadcasts them, NCCL over NVLink
+    on GPUs), kernels then read local memory only.
+
+    A causal row never looks past its own chunk, so chunk c is computed exactly by the unchanged single-GPU
+    call on q[chunk c] against k/v[: end of chunk c] (queries aligned to the end of the keys, which is the
+    layout the path already supports for prefill against a cache): same block offsets, same first-chunk rule,
+    same normalisation as in the one-GPU run.  Returns {chunk index: output [B,Hq,rows,D]} for the local chunks.
+    q_len must equal k_len and be a multiple of chunk_size."""
+    if broadcast_kv_from is not None:
+        import torch.distributed as dist
+        dist.broadcast(key_states, src=broadcast_kv_from, group=group)
+        dist.broadcast(value_states, src=broadcast_kv_from, group=group)
+    L = query_states.shape[2]
+    if key_states.shape[2] != L or L % chunk_size != 0:
+        raise ValueError("query-chunk sharding needs q_len == k_len, a multiple of chunk_size")
+    out = {}
+    for c in shard_query_chunks(L // chunk_size, world_size, rank):
+        r0, r1 = c * chunk_size, (c + 1) * chunk_size
+        out[c] = prefill_fn(query_states[:, :, r0:r1], key_states[:, :, :r1], value_states[:, :, :r1],
+                            threshold=threshold, chunk_size=chunk_size, causal=True, **kwargs)
+    return out
