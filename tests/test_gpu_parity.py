@@ -455,6 +455,64 @@ def test_prefill_against_a_longer_key_cache():
     assert err.max() < OUT_MAX_ABS and err.mean() < OUT_MEAN_ABS, (err.max(), err.mean())
 
 
+def test_llama_attention_core_prefill_decode_and_gqa():
+    """The Llama integration core: prefill equals Xattention_prefill on repeated K/V with the layer's per-head
+    thresholds; decode (one query against the cache) and the dense metric equal SDPA."""
+    import xattn_b200
+    from xattn_b200 import synth
+    from xattn_b200.llama_shim import FastPrefillConfig, attention_core
+    q, k, v, w = synth.make_inputs("llama3_8b_32k", seed=13, heads_limit=2, seq_len=4096)
+    dq, dk, dv = q.to(DEV), k.to(DEV), v.to(DEV)
+    table = torch.rand(3, 8) * 0.4 + 0.55
+    cfg = FastPrefillConfig(threshold=table, stride=8)
+    got = attention_core(dq, dk, dv, 1, cfg)
+    want = xattn_b200.Xattention_prefill(dq, dk.repeat_interleave(4, 1), dv.repeat_interleave(4, 1), 8,
+                                         threshold=table[1].to(DEV))
+    assert torch.equal(got, want)
+    # decode step: the newest query against all keys
+    o = attention_core(dq[:, :, -1:], dk, dv, 0, cfg)
+    ref = torch.nn.functional.scaled_dot_product_attention(dq[:, :, -1:].float(), dk.float().repeat_interleave(4, 1),
+                                                           dv.float().repeat_interleave(4, 1))
+    assert (o.float() - ref).abs().max() < OUT_MAX_ABS
+    full = attention_core(dq, dk, dv, 0, FastPrefillConfig(metric="full"))
+    ref = torch.nn.functional.scaled_dot_product_attention(dq.float(), dk.float().repeat_interleave(4, 1),
+                                                           dv.float().repeat_interleave(4, 1), is_causal=True)
+    err = (full.float() - ref).abs()
+    assert err.max() < OUT_MAX_ABS and err.mean() < OUT_MEAN_ABS
+
+
+def test_dit_varlen_wrapper_ragged_lengths():
+    """The video-diffusion call pattern: a valid segment whose length is no multiple of 128 (or of the stride)
+    through non-causal XAttention, a padded text tail dense; threshold >= 1 switches the first to dense."""
+    from xattn_b200 import synth
+    from xattn_b200.dit_shim import xattn_varlen_attention
+    g = torch.Generator().manual_seed(21)
+    q, k, v = synth.dit_like(g, 2, frames=2, rows=20, cols=32, text_tokens=256, pad_to=1)
+    valid = 1280 + 75                       # image tokens + 75 real text tokens
+    q, k, v = q.bfloat16().to(DEV), k.bfloat16().to(DEV), v.bfloat16().to(DEV)
+    total = q.shape[2]
+    cu = torch.tensor([0, valid, total], dtype=torch.int32)
+    dense = xattn_varlen_attention(q, k, v, cu, cu, threshold=1.0)
+    ref = torch.cat([
+        torch.nn.functional.scaled_dot_product_attention(q[:, :, :valid].float(), k[:, :, :valid].float(), v[:, :, :valid].float()),
+        torch.nn.functional.scaled_dot_product_attention(q[:, :, valid:].float(), k[:, :, valid:].float(), v[:, :, valid:].float())], 2)
+    err = (dense.float() - ref).abs()
+    assert dense.shape == q.shape and err.max() < OUT_MAX_ABS and err.mean() < OUT_MEAN_ABS
+    sparse = xattn_varlen_attention(q, k, v, cu, cu, threshold=0.95, stride=8)
+    # the tail is dense in both; the valid part must equal the oracle's attention under the oracle-checked mask
+    assert torch.equal(sparse[:, :, valid:], dense[:, :, valid:])
+    qc, kc, vc = q[:, :, :valid].cpu(), k[:, :, :valid].cpu(), v[:, :, :valid].cpu()
+    chunk = orc.default_chunk_size(valid)
+    _, omask = orc.xattn_estimate_oracle(qc.float(), kc.float(), 128, 8, 1.0, 0.95, chunk, False)
+    import xattn_b200
+    _, gmask = xattn_b200.xattn_estimate(q[:, :, :valid].contiguous(), k[:, :, :valid].contiguous(), 128, 8,
+                                         threshold=0.95, chunk_size=chunk, causal=False)
+    assert int((gmask.cpu() != omask).sum()) <= max(2, int(5e-3 * omask.numel()))
+    refs = orc.block_sparse_attention_oracle(qc, kc, vc, gmask.cpu(), False)
+    err = (sparse[:, :, :valid].float().cpu() - refs).abs()
+    assert err.max() < OUT_MAX_ABS and err.mean() < OUT_MEAN_ABS, (err.max(), err.mean())
+
+
 def test_runs_are_bit_identical():
     """Same inputs, two runs: identical bits (no race between the roles of a CTA)."""
     import xattn_b200
