@@ -35,6 +35,9 @@ import torch  # noqa: E402
 
 METRIC = "prefill_attention_effective_tflops"
 UNIT = "TFLOP/s (dense-equivalent, 4*Lq*Lk*D*Hq/2 causal)"
+# dram__bytes_read.sum + dram__bytes_write.sum of one block_sparse_attn_kernel launch, from the ncu capture that
+# profiles/block_sparse_attn_kernel_llama3_8b_32k.md summarises (406.9 MB + 233.2 MB); other workloads: not captured
+NCU_ATTENTION_TRAFFIC_BYTES = {"llama3_8b_32k": 640_080_640}
 DEFAULT_WORKLOAD = "llama3_8b_32k"
 
 
@@ -281,7 +284,10 @@ def run_gpu_arm(args):
     peaks = measured_peaks()
     att_tflops = f_att / (ph[2] * 1e-3) / 1e12 if ph[2] > 0 else 0.0
     roofline = dict(bound="tensor", kernel="block_sparse_attn_kernel", achieved=att_tflops, peak=peaks["bf16"],
-                    unit="TFLOP/s", frac=att_tflops / peaks["bf16"], traffic=None, peak_source=peaks["source"],
+                    unit="TFLOP/s", frac=att_tflops / peaks["bf16"],
+                    traffic=NCU_ATTENTION_TRAFFIC_BYTES.get(args.workload), traffic_unit="bytes per launch (ncu)",
+                    algorithmic_bytes=(2 * w.hq + 2 * w.hkv) * w.seq_len * w.head_dim * 2,   # Q+O, K+V once; 16-bit
+                    peak_source=peaks["source"],
                     executed_flops_per_launch=f_att, selected_blocks=n_sel)
 
     # the same attention kernel on a dense causal mask (long block lists): what the inner loop sustains when the
