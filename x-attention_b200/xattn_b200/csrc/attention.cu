@@ -82,8 +82,12 @@ __device__ __forceinline__ void xb_trace(int* status, uint32_t& n, int role, uin
 #define XB_TRACE_EV(tag, val) ((void)0)
 #endif
 
-template <int N> __device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
-template <int N> __device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+// Register budget of a role.  The kernel is launched with 512 threads x 128 registers; setmaxnreg moves registers
+// between warpgroups inside that allocation (8 x softmax + 4 x epilogue + 4 x load/MMA warps = 2048 per lane).
+template <int N> __device__ __forceinline__ void reg_set() {
+  if constexpr (N > 128) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+  if constexpr (N < 128) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
 
 // Work item t -> (b, h, qb): heaviest query blocks (largest index) first, the heads of a kv group adjacent.
 struct Item {
@@ -136,6 +140,14 @@ block_sparse_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
                          const __grid_constant__ CUtensorMap tmVf, const AttnParams p,
                          const int32_t* __restrict__ block_idx, const int32_t* __restrict__ block_cnt,
                          void* __restrict__ out, int* status) {
+  // Shared memory takes nearly the whole L1, so a register spilled to local memory costs an L2 round trip:
+  // the split below is the one with which ptxas reports no spill for any role of this instantiation.
+#ifdef XB_A_SM
+  constexpr int kRegSoftmax = XB_A_SM, kRegEpilogue = XB_A_EP, kRegLoadMma = XB_A_LM;
+#else
+  constexpr int kRegSoftmax = 152, kRegEpilogue = 112, kRegLoadMma = 96;
+#endif
+  static_assert(8 * kRegSoftmax + 4 * kRegEpilogue + 4 * kRegLoadMma <= 16 * 128, "register budget of the roles");
   extern __shared__ __align__(1024) uint8_t smem[];
   // tiles: [stream][Q, K, V]
   float* s_l = reinterpret_cast<float*>(smem + kAttnSmemTiles);          // [stream][2][128] final row sums
@@ -227,7 +239,7 @@ block_sparse_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
   const int group = p.hq / p.hkv;
 
   if (warp >= 12) {
-    reg_dec<96>();
+    reg_set<kRegLoadMma>();
     const int s = (warp - 12) >> 1;                   // stream of this warp
     uint8_t* tiles = smem + s * 3 * kTile16;          // Q, K, V tiles of the stream
     if ((warp & 1) == 0) {
@@ -420,7 +432,7 @@ block_sparse_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
     }
   } else if (warp < 8) {
     // -------------------------------------------------------------------- softmax of stream (warp >> 2)
-    reg_inc<144>();
+    reg_set<kRegSoftmax>();
     if constexpr (kHalf) {
     const int s = warp >> 2;
     const int quad = warp & 3;
@@ -777,7 +789,7 @@ block_sparse_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
     }
   } else {
     // -------------------------------------------------------------------- epilogue (warps 8-11), both streams
-    reg_dec<128>();
+    reg_set<kRegEpilogue>();
     const int quad = warp & 3;
     const int r = quad * 32 + lane;
     const uint32_t lane_bits = static_cast<uint32_t>(quad * 32) << 16;
@@ -817,46 +829,57 @@ block_sparse_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
       const int q_row0 = it.qb * 128 + quad * 32;                     // first row of this warp
       uint8_t* obase = static_cast<uint8_t*>(out) +
                        2 * (static_cast<int64_t>(it.b) * p.osb + static_cast<int64_t>(it.h) * p.osh);
-      // O leaves tensor memory first (scaled and packed to 16 bit: 64 registers) so that the stream's next item
-      // can start accumulating while this one is still being stored
-      uint4 packed[16];
-#pragma unroll
-      for (int c2 = 0; c2 < 2; ++c2) {
+      // O leaves tensor memory first, half by half (scaled and packed to 16 bit; the first half is parked in the
+      // staging buffer, the second in registers), so that the stream's next item can start accumulating while
+      // this one is still being stored
+      auto load_half = [&](int half, uint4 (&pk)[8]) {
         uint32_t v0[32], v1[32];
-        tmem_ld32(tmem_o + c2 * 64, v0);
-        tmem_ld32(tmem_o + c2 * 64 + 32, v1);
+        tmem_ld32(tmem_o + half * 64, v0);
+        tmem_ld32(tmem_o + half * 64 + 32, v1);
         tc_wait_ld();
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
-          packed[c2 * 8 + q4] = make_uint4(
+          pk[q4] = make_uint4(
               pack16(__uint_as_float(v0[q4 * 8 + 0]) * inv, __uint_as_float(v0[q4 * 8 + 1]) * inv, p.is_bf16),
               pack16(__uint_as_float(v0[q4 * 8 + 2]) * inv, __uint_as_float(v0[q4 * 8 + 3]) * inv, p.is_bf16),
               pack16(__uint_as_float(v0[q4 * 8 + 4]) * inv, __uint_as_float(v0[q4 * 8 + 5]) * inv, p.is_bf16),
               pack16(__uint_as_float(v0[q4 * 8 + 6]) * inv, __uint_as_float(v0[q4 * 8 + 7]) * inv, p.is_bf16));
-          packed[c2 * 8 + 4 + q4] = make_uint4(
+          pk[4 + q4] = make_uint4(
               pack16(__uint_as_float(v1[q4 * 8 + 0]) * inv, __uint_as_float(v1[q4 * 8 + 1]) * inv, p.is_bf16),
               pack16(__uint_as_float(v1[q4 * 8 + 2]) * inv, __uint_as_float(v1[q4 * 8 + 3]) * inv, p.is_bf16),
               pack16(__uint_as_float(v1[q4 * 8 + 4]) * inv, __uint_as_float(v1[q4 * 8 + 5]) * inv, p.is_bf16),
               pack16(__uint_as_float(v1[q4 * 8 + 6]) * inv, __uint_as_float(v1[q4 * 8 + 7]) * inv, p.is_bf16));
         }
-      }
-      tc_fence_before();
-      mbar_arrive(bar(s, O_EMPTY));
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
+      };
+      auto stage = [&](const uint4 (&pk)[8]) {
 #pragma unroll
         for (int chunk = 0; chunk < 8; ++chunk)
-          *reinterpret_cast<uint4*>(stg + lane * 128 + ((chunk ^ (lane & 7)) << 4)) = packed[half * 8 + chunk];
-        __syncwarp();
+          *reinterpret_cast<uint4*>(stg + lane * 128 + ((chunk ^ (lane & 7)) << 4)) = pk[chunk];
+      };
+      auto store_half = [&](int half) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int rr = 4 * i + (lane >> 3);                         // row within the warp's 32
+        for (int i2 = 0; i2 < 8; ++i2) {
+          const int rr = 4 * i2 + (lane >> 3);                        // row within the warp's 32
           const int chunk = lane & 7;
           const uint4 wv = *reinterpret_cast<const uint4*>(stg + rr * 128 + ((chunk ^ (rr & 7)) << 4));
           const int q_pos_r = q_row0 + rr;
           if (q_pos_r < p.q_len)
             *reinterpret_cast<uint4*>(obase + 2 * static_cast<int64_t>(q_pos_r) * p.osl + half * 128 + chunk * 16) = wv;
         }
+      };
+      {
+        uint4 pk[8];
+        load_half(0, pk);
+        stage(pk);
+        load_half(1, pk);
+        tc_fence_before();
+        mbar_arrive(bar(s, O_EMPTY));
+        __syncwarp();
+        store_half(0);
+        __syncwarp();
+        stage(pk);
+        __syncwarp();
+        store_half(1);
         __syncwarp();
       }
       if (threadIdx.x == 256) XB_TRACE_EV(0x44 + s, m);
