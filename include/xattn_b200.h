@@ -128,6 +128,22 @@ int xattn_b200_split_f32(const float* x, int batch, int heads, int len, int head
                          int64_t stride_h, int64_t stride_l, int role, void* out, void* cuda_stream);
 
 /*
+ * Rotary position embedding, applied in place to the query and key projections in one launch.
+ * Replaces apply_rotary_pos_emb (xattn/src/load_llama.py:34-65, called at :142 and :356):
+ *   x' = x*cos + rotate_half(x)*sin, with each product and the sum rounded to the 16-bit storage type exactly
+ *   as the reference's three tensor operations round them (results are bit-identical).
+ * q: [batch, hq, len, head_dim], k: [batch, hkv, len, head_dim], element strides, unit stride on head_dim --
+ * typically the [batch, len, heads*head_dim] projection outputs seen through strides, so that no transposed
+ * copy is made before the estimate and attention kernels (which take the same strided views).
+ * cos, sin: [batch, len, head_dim] in the same dtype (stride_b may be 0 for one table shared by the batch).
+ * head_dim a multiple of 16; bases 16-byte aligned; strides multiples of 8 elements.
+ */
+int xattn_b200_rope_qk(void* q, void* k, int dtype, int batch, int hq, int hkv, int len, int head_dim,
+                       int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_l, int64_t k_stride_b,
+                       int64_t k_stride_h, int64_t k_stride_l, const void* cos, const void* sin,
+                       int64_t cs_stride_b, int64_t cs_stride_l, void* cuda_stream);
+
+/*
  * Phase 2 -- threshold block selection for all query chunks at once.
  * Replaces find_blocks_chunked (xattn/src/utils.py:44-191, prefill branch :87-172) as called per
  * chunk by xattn_estimate (xattn/src/Xattention.py:255-263), plus the mask post-processing of

@@ -16,6 +16,9 @@ This module restates, on the CPU in fp32/fp64 torch ops, what the reference proj
                                                      statement of the same math for the causal
                                                      case is xattn/src/Flexprefill.py:12-44).
 
+  * the rotary embedding of the Llama patch          (xattn/src/load_llama.py:34-65; pinned against
+                                                     the reference function, tests/golden/rope.npz).
+
 Nothing in the shipped package may import this module: only ``tests/``, the smoke check and
 the CPU-baseline leg of ``bench.py`` do, and only as the checker or as the timed baseline.
 
@@ -364,3 +367,22 @@ def block_sparse_attention_oracle(
                 p = torch.nan_to_num(torch.softmax(s, dim=-1), nan=0.0)
                 out[b, h, r0:r1] = p @ vv
     return out
+
+
+def apply_rotary_pos_emb_oracle(q: torch.Tensor, k: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor):
+    """Rotary embedding as the reference's Llama patch applies it (xattn/src/load_llama.py:34-65): per head
+    row x of width D, x' = x*cos + rot(x)*sin with rot(x)[i] = -x[i + D/2] for i < D/2, x[i - D/2] otherwise.
+    The reference evaluates this as 16-bit tensor operations; each of them computes in fp32 and rounds to the
+    storage type, which is restated here explicitly.  q [B,Hq,L,D], k [B,Hkv,L,D], cos/sin [B,L,D]."""
+    def one(x):
+        dt = x.dtype
+        half = x.shape[-1] // 2
+        xf = x.float()
+        c, s = cos.float()[:, None], sin.float()[:, None]
+        rot = torch.empty_like(xf)
+        rot[..., :half] = -xf[..., half:]
+        rot[..., half:] = xf[..., :half]
+        a = (xf * c).to(dt).float()
+        b = (rot * s).to(dt).float()
+        return (a + b).to(dt)
+    return one(q), one(k)

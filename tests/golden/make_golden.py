@@ -105,8 +105,33 @@ TRITON_CASES = [
 ]
 
 
+# rotary embedding applied to the projection outputs (xattn/src/load_llama.py:34-65, call site :142)
+ROPE_CASES = [
+    dict(dtype="bf16", batch=1, hq=4, hkv=2, length=40, head_dim=128, seed=9001),
+    dict(dtype="fp16", batch=2, hq=2, hkv=1, length=17, head_dim=128, seed=9002),
+    dict(dtype="bf16", batch=1, hq=3, hkv=3, length=9, head_dim=64, seed=9003),
+]
+
+
+def rope_inputs(spec):
+    """q [B,Hq,L,D], k [B,Hkv,L,D] (views of [B,L,H,D] storage, as the projections leave them) and cos/sin [B,L,D]
+    built the way Llama's rotary module does (fp32 angles, cast to the model dtype)."""
+    import torch
+    dt = {"bf16": torch.bfloat16, "fp16": torch.float16}[spec["dtype"]]
+    g = torch.Generator().manual_seed(spec["seed"])
+    B, L, D = spec["batch"], spec["length"], spec["head_dim"]
+    q = torch.randn(B, L, spec["hq"], D, generator=g).to(dt).transpose(1, 2)
+    k = torch.randn(B, L, spec["hkv"], D, generator=g).to(dt).transpose(1, 2)
+    pos = (torch.arange(L)[None, :] + torch.randint(0, 5000, (B, 1), generator=g)).float()
+    inv_freq = 1.0 / (500000.0 ** (torch.arange(0, D, 2).float() / D))
+    ang = pos[:, :, None] * inv_freq[None, None, :]
+    emb = torch.cat((ang, ang), dim=-1)
+    return q, k, emb.cos().to(dt), emb.sin().to(dt)
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--rope-only", action="store_true", help="only (re)generate the rotary-embedding fixture")
     ap.add_argument("--reference", default="/root/reference")
     ap.add_argument("--triton", action="store_true", help="also (re)generate the Triton-interpreter fixtures")
     args = ap.parse_args()
@@ -130,6 +155,20 @@ def main():
     torch.Tensor.to = _to
     from xattn.src.Xattention import xattn_estimate
     from xattn.src.utils import find_blocks_chunked
+
+    # rotary embedding: the reference's own function on the same inputs; 16-bit values stored as their bits
+    from xattn.src.load_llama import apply_rotary_pos_emb
+    out = {}
+    for i, spec in enumerate(ROPE_CASES):
+        q, k, cos, sin = rope_inputs(spec)
+        qe, ke = apply_rotary_pos_emb(q, k, cos, sin)
+        out[f"q_{i}"] = qe.contiguous().view(torch.int16).numpy()
+        out[f"k_{i}"] = ke.contiguous().view(torch.int16).numpy()
+    out["specs"] = np.array(json.dumps(ROPE_CASES))
+    np.savez_compressed(os.path.join(HERE, "rope.npz"), **out)
+    print("rope cases:", len(ROPE_CASES))
+    if args.rope_only:
+        return
 
     def run(spec, use_triton):
         q, k = case_inputs(spec)

@@ -513,6 +513,71 @@ def test_dit_varlen_wrapper_ragged_lengths():
     assert err.max() < OUT_MAX_ABS and err.mean() < OUT_MEAN_ABS, (err.max(), err.mean())
 
 
+def test_rotary_embedding_matches_reference_fixture_bit_for_bit():
+    import xattn_b200
+    from xattn_b200 import ops
+    from make_golden import rope_inputs
+    z, specs = _load("rope.npz")
+    for i, spec in enumerate(specs):
+        q, k, cos, sin = rope_inputs(spec)
+        # device copies that keep the [B, L, H, D] storage behind the [B, H, L, D] views
+        qd = q.transpose(1, 2).contiguous().to(DEV).transpose(1, 2)
+        kd = k.transpose(1, 2).contiguous().to(DEV).transpose(1, 2)
+        ops.apply_rotary_pos_emb_(qd, kd, cos.to(DEV), sin.to(DEV))
+        xattn_b200.check_device_status()
+        assert np.array_equal(qd.cpu().contiguous().view(torch.int16).numpy(), z[f"q_{i}"]), spec
+        assert np.array_equal(kd.cpu().contiguous().view(torch.int16).numpy(), z[f"k_{i}"]), spec
+
+
+def _rope_table(L, D, dtype):
+    ang = torch.arange(L).float()[:, None] / (500000.0 ** (torch.arange(0, D, 2).float() / D))[None, :]
+    emb = torch.cat((ang, ang), -1)[None]                                 # [1, L, D]: one table for the batch
+    return emb.cos().to(dtype), emb.sin().to(dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_rotary_embedding_vs_oracle_larger_and_shared_table(dtype):
+    from xattn_b200 import ops
+    g = torch.Generator().manual_seed(77)
+    B, Hq, Hkv, L, D = 2, 8, 2, 1000, 128
+    q = torch.randn(B, L, Hq, D, generator=g).to(dtype).transpose(1, 2)
+    k = torch.randn(B, L, Hkv, D, generator=g).to(dtype).transpose(1, 2)
+    cos, sin = _rope_table(L, D, dtype)
+    want_q, want_k = orc.apply_rotary_pos_emb_oracle(q, k, cos, sin)
+    qd = q.transpose(1, 2).contiguous().to(DEV).transpose(1, 2)
+    kd = k.transpose(1, 2).contiguous().to(DEV).transpose(1, 2)
+    ops.apply_rotary_pos_emb_(qd, kd, cos.to(DEV), sin.to(DEV))
+    assert torch.equal(qd.cpu(), want_q) and torch.equal(kd.cpu(), want_k)
+    # contiguous [B, H, L, D] storage works as well
+    qc, kc = q.contiguous().to(DEV), k.contiguous().to(DEV)
+    ops.apply_rotary_pos_emb_(qc, kc, cos.to(DEV), sin.to(DEV))
+    assert torch.equal(qc.cpu(), want_q) and torch.equal(kc.cpu(), want_k)
+
+
+def test_llama_rope_and_attend_equals_the_composed_reference_steps():
+    import xattn_b200
+    from xattn_b200 import llama_shim, synth
+    L = 2048
+    q, k, v, w = synth.make_inputs("llama3_8b_32k", seed=5, heads_limit=2, seq_len=L)
+    B, Hq, _, D = q.shape
+    Hkv = k.shape[1]
+    # projection outputs [B, L, H*D]
+    qp = q.transpose(1, 2).reshape(B, L, Hq * D).contiguous().to(DEV)
+    kp = k.transpose(1, 2).reshape(B, L, Hkv * D).contiguous().to(DEV)
+    vp = v.transpose(1, 2).reshape(B, L, Hkv * D).contiguous().to(DEV)
+    cos, sin = _rope_table(L, D, q.dtype)
+    cfg = llama_shim.FastPrefillConfig(threshold=0.9, stride=8, num_layers=1, num_heads=Hq, device=DEV)
+    # the reference's sequence of steps, each on its own tensors
+    q_ref, k_ref = orc.apply_rotary_pos_emb_oracle(q, k, cos, sin)
+    want = llama_shim.attention_core(q_ref.to(DEV), k_ref.to(DEV), v.to(DEV), 0, cfg)
+    want = want.transpose(1, 2).contiguous().reshape(B, L, Hq * D)
+    got = llama_shim.rope_and_attend(qp, kp, vp, cos.to(DEV), sin.to(DEV), Hq, Hkv, 0, cfg)
+    xattn_b200.check_device_status()
+    assert got.shape == (B, L, Hq * D) and got.is_contiguous()
+    assert torch.equal(got, want)
+    assert torch.equal(kp.view(B, L, Hkv, D).transpose(1, 2).cpu(), k_ref)     # rotated keys left for the cache
+
+
 def test_runs_are_bit_identical():
     """Same inputs, two runs: identical bits (no race between the roles of a CTA)."""
     import xattn_b200

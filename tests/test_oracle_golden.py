@@ -7,7 +7,7 @@ import numpy as np
 import pytest
 import torch
 
-from make_golden import case_inputs
+from make_golden import case_inputs, rope_inputs
 from oracle import xattn_oracle as orc
 
 GOLD = os.path.join(os.path.dirname(__file__), "golden")
@@ -100,3 +100,13 @@ def test_attention_oracle_dense_equals_sdpa():
         ref = torch.nn.functional.scaled_dot_product_attention(
             q, k.repeat_interleave(2, 1), v.repeat_interleave(2, 1), is_causal=causal)
         assert torch.allclose(o, ref, atol=2e-5, rtol=1e-4)
+
+
+def test_rotary_embedding_oracle_matches_the_reference_function_bit_for_bit():
+    z, specs = _load("rope.npz")
+    assert len(specs) >= 3
+    for i, spec in enumerate(specs):
+        q, k, cos, sin = rope_inputs(spec)
+        qe, ke = orc.apply_rotary_pos_emb_oracle(q, k, cos, sin)
+        assert np.array_equal(qe.contiguous().view(torch.int16).numpy(), z[f"q_{i}"]), spec
+        assert np.array_equal(ke.contiguous().view(torch.int16).numpy(), z[f"k_{i}"]), spec

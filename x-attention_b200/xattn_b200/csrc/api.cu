@@ -9,6 +9,9 @@ int estimate_launch(const void* q, const void* k, int dtype, int batch, int hq, 
                     float* attn_sums, void* workspace, size_t workspace_bytes, int* status, cudaStream_t stream);
 int split_f32_launch(const float* x, int batch, int heads, int len, int head_dim, int64_t sb, int64_t sh, int64_t sl,
                      int role, void* out, cudaStream_t stream);
+int rope_qk_launch(void* q, void* k, int dtype, int batch, int hq, int hkv, int len, int head_dim, int64_t qsb,
+                   int64_t qsh, int64_t qsl, int64_t ksb, int64_t ksh, int64_t ksl, const void* cos, const void* sin,
+                   int64_t cs_stride_b, int64_t cs_stride_l, cudaStream_t stream);
 int select_launch(const float* attn_sums, int batch, int heads, int q_blocks, int k_blocks, int bpc, int block_offset,
                   int causal, int diagonal_cleanup, double threshold, const float* thr_per_head, int keep_sink,
                   int keep_recent, uint8_t* mask, int32_t* block_idx, int32_t* block_cnt, int list_q_blocks,
@@ -81,6 +84,15 @@ int xattn_b200_split_f32(const float* x, int batch, int heads, int len, int head
                          int64_t stride_h, int64_t stride_l, int role, void* out, void* cuda_stream) {
   return xb::split_f32_launch(x, batch, heads, len, head_dim, stride_b, stride_h, stride_l, role, out,
                               static_cast<cudaStream_t>(cuda_stream));
+}
+
+int xattn_b200_rope_qk(void* q, void* k, int dtype, int batch, int hq, int hkv, int len, int head_dim,
+                       int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_l, int64_t k_stride_b,
+                       int64_t k_stride_h, int64_t k_stride_l, const void* cos, const void* sin,
+                       int64_t cs_stride_b, int64_t cs_stride_l, void* cuda_stream) {
+  return xb::rope_qk_launch(q, k, dtype, batch, hq, hkv, len, head_dim, q_stride_b, q_stride_h, q_stride_l,
+                            k_stride_b, k_stride_h, k_stride_l, cos, sin, cs_stride_b, cs_stride_l,
+                            static_cast<cudaStream_t>(cuda_stream));
 }
 
 int xattn_b200_select(const float* attn_sums, int batch, int heads, int q_blocks, int k_blocks,

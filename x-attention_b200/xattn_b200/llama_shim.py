@@ -59,3 +59,28 @@ def attention_core(query_states: torch.Tensor, key_states: torch.Tensor, value_s
     # decode, or dense prefill: every key block that a row may see (token-level causal inside the kernel)
     idx, cnt = _dense_lists(B, Hq, q_len, k_len, query_states.device)
     return ops.block_sparse_attention(query_states, key_states, value_states, idx, cnt, causal=True)
+
+
+def rope_and_attend(q_proj_out: torch.Tensor, k_proj_out: torch.Tensor, v_proj_out: torch.Tensor,
+                    cos: torch.Tensor, sin: torch.Tensor, num_heads: int, num_key_value_heads: int,
+                    layer_idx: int, config: FastPrefillConfig) -> torch.Tensor:
+    """The steps either side of the attention core, without their copies (prefill, no earlier cache).
+
+    The reference reshapes the projection outputs [B, L, H*D] to [B, H, L, D] views, applies the rotary embedding
+    out of place (three full-size temporaries per tensor, xattn/src/load_llama.py:124-142), repeats K/V, and
+    after attention makes `attn_output.transpose(1, 2).contiguous()` before `o_proj` (:211-213).  Here the rotary
+    embedding is one in-place kernel on the projection outputs, the estimate and attention kernels read the
+    [B, H, L, D] views through their strides, and the attention output is written as [B, L, H, D], so the
+    returned [B, L, H*D] tensor is what `o_proj` consumes: no transposed copy on either side.
+    `q_proj_out` and `k_proj_out` are overwritten with their rotated values (the key cache wants those)."""
+    B, L, _ = q_proj_out.shape
+    D = q_proj_out.shape[2] // num_heads
+    q = q_proj_out.view(B, L, num_heads, D).transpose(1, 2)
+    k = k_proj_out.view(B, L, num_key_value_heads, D).transpose(1, 2)
+    v = v_proj_out.view(B, L, num_key_value_heads, D).transpose(1, 2)
+    ops.apply_rotary_pos_emb_(q, k, cos, sin)
+    out = attention_core(q, k, v, layer_idx, config)               # [B, Hq, L, D] view of [B, L, Hq, D] storage
+    out_blhd = out.transpose(1, 2)
+    if not out_blhd.is_contiguous():                               # never for this package's kernels
+        out_blhd = out_blhd.contiguous()
+    return out_blhd.reshape(B, L, num_heads * D)

@@ -190,6 +190,28 @@ def select_blocks(sums: torch.Tensor, blocks_per_chunk: int, block_offset: int,
     return (mask.view(torch.bool) if mask is not None else None), idx, cnt
 
 
+def apply_rotary_pos_emb_(q: torch.Tensor, k: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> None:
+    """In-place rotary embedding of q [B,Hq,L,D] and k [B,Hkv,L,D] (any strides, unit stride on D) with
+    cos/sin [B,L,D] (or [1,L,D]) of the same 16-bit dtype: bit-identical to the reference's
+    `apply_rotary_pos_emb` (xattn/src/load_llama.py:41-65), one launch for both tensors."""
+    _require_cuda(q, k, cos, sin)
+    if q.dtype not in _DT or k.dtype != q.dtype or cos.dtype != q.dtype or sin.dtype != q.dtype:
+        raise ValueError("apply_rotary_pos_emb_: q, k, cos, sin must share one 16-bit dtype (bf16 or fp16)")
+    B, Hq, L, D = q.shape
+    Hkv = k.shape[1]
+    if k.shape != (B, Hkv, L, D):
+        raise ValueError("apply_rotary_pos_emb_: q and k must share batch, length and head_dim")
+    if cos.dim() != 3 or cos.shape[1:] != (L, D) or cos.shape[0] not in (1, B) or sin.shape != cos.shape:
+        raise ValueError("apply_rotary_pos_emb_: cos/sin must be [batch or 1, len, head_dim]")
+    if cos.stride(2) != 1 or sin.stride(2) != 1 or sin.stride() != cos.stride():
+        cos, sin = cos.contiguous(), sin.contiguous()
+    cs_b = cos.stride(0) if cos.shape[0] == B and B > 1 else 0
+    lib = _lib.load()
+    _lib.check(lib.xattn_b200_rope_qk(q.data_ptr(), k.data_ptr(), _DT[q.dtype], B, Hq, Hkv, L, D, *_strides3(q),
+                                      *_strides3(k), cos.data_ptr(), sin.data_ptr(), cs_b, cos.stride(1),
+                                      _stream(q)), "rope_qk")
+
+
 def mask_to_lists(mask: torch.Tensor, q_len: int, k_len: int, causal: bool):
     _require_cuda(mask)
     lib = _lib.load()
