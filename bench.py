@@ -211,8 +211,10 @@ def run_gpu_arm(args):
     device = torch.device("cuda", local)
     torch.cuda.set_device(device)
     import xattn_b200
-    from xattn_b200 import ops, synth
+    from xattn_b200 import host_pipeline, ops, synth
 
+    # host buffers of this rank on the NUMA node of its GPU (matters for the host-buffer leg with several ranks)
+    numa_cores = host_pipeline.bind_host_to_gpu(device)
     q, k, v, w = synth.make_inputs(args.workload, seed=rank)
     chunk = w.chunk_size or ops.default_chunk_size(w.seq_len)
     hq_pin, k_pin, v_pin = q.pin_memory(), k.pin_memory(), v.pin_memory()
@@ -342,7 +344,8 @@ def run_gpu_arm(args):
             metric=METRIC, value=value, unit=UNIT, n_gpus=n, steps=args.steps, warmup=args.warmup, ms_per_step=ms,
             higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16", data="synthetic",
             config=_config(w, chunk, n), clocks=clocks,
-            e2e=dict(value=e2e_value, unit=UNIT, ms_per_step=ms_e2e, h2d_bytes_per_step=bi, d2h_bytes_per_step=bo),
+            e2e=dict(value=e2e_value, unit=UNIT, ms_per_step=ms_e2e, h2d_bytes_per_step=bi, d2h_bytes_per_step=bo,
+                     host_cores_bound=len(numa_cores) if numa_cores else None),
             gpu_launches=7 * args.steps,
             kernels_per_step=["est_setup_kernel", "est_gemm_kernel", "est_rowstat_kernel", "est_blocksum_kernel",
                               "select_kernel", "block_sparse_attn_kernel<false>", "block_sparse_attn_kernel<true>"],

@@ -19,6 +19,30 @@ from . import ops
 _copy_streams = {}
 
 
+def bind_host_to_gpu(device: Union[int, str, torch.device]) -> Optional[list]:
+    """Restrict the calling process to the CPU cores next to `device` (NVML's CPU affinity of that GPU), so that
+    host buffers allocated and first touched afterwards sit on the GPU's NUMA node and copies over PCIe do not
+    cross the socket interconnect.  One process per GPU should call this before it allocates pinned memory.
+    Changes nothing on the GPU.  Returns the core list, or None when the affinity cannot be read."""
+    import os
+    dev = torch.device("cuda", device) if isinstance(device, int) else torch.device(device)
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        uuid = str(torch.cuda.get_device_properties(dev).uuid)
+        handle = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid).encode() if not uuid.startswith("GPU-") else uuid.encode())
+        words = (os.cpu_count() + 63) // 64
+        mask = pynvml.nvmlDeviceGetCpuAffinity(handle, words)
+        cpus = [64 * i + b for i, m in enumerate(mask) for b in range(64) if (int(m) >> b) & 1]
+        allowed = sorted(set(cpus) & set(os.sched_getaffinity(0)))
+        if not allowed:
+            return None
+        os.sched_setaffinity(0, allowed)
+        return allowed
+    except Exception:                                   # no NVML, no such call, container without the cores
+        return None
+
+
 def _streams(device: torch.device):
     key = device.index
     s = _copy_streams.get(key)
