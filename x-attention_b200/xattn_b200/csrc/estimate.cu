@@ -62,7 +62,8 @@ __host__ __device__ inline void row_bounds(const EstGeom& g, int i, int& lo, int
 }
 
 // tile_lo[mt], tile_prefix[mt] (exclusive prefix of tile counts, n_mtiles+1 entries)
-__global__ void est_setup_kernel(EstGeom g, int* __restrict__ tile_lo, int* __restrict__ tile_prefix) {
+__global__ void est_setup_kernel(EstGeom g, int* __restrict__ tile_lo, int* __restrict__ tile_prefix,
+                                 int* __restrict__ pair_lo, int* __restrict__ pair_prefix) {
   extern __shared__ int s_cnt[];
   for (int mt = threadIdx.x; mt < g.n_mtiles; mt += blockDim.x) {
     // lo(i) and hi(i) never decrease with i, so the tile's column range is [lo(first row), hi(last valid row)]
@@ -92,15 +93,30 @@ __global__ void est_setup_kernel(EstGeom g, int* __restrict__ tile_lo, int* __re
       acc += s_cnt[mt];
     }
     tile_prefix[g.n_mtiles] = acc;
+    // pairs of row tiles (2p, 2p+1) for the CTA-pair GEMM: the union of their column-tile ranges
+    const int n_pairs = (g.n_mtiles + 1) / 2;
+    acc = 0;
+    for (int pm = 0; pm < n_pairs; ++pm) {
+      int lo = 0x7fffffff, hi = -1;
+      for (int mt = 2 * pm; mt < 2 * pm + 2 && mt < g.n_mtiles; ++mt)
+        if (s_cnt[mt] > 0) {
+          lo = tile_lo[mt] < lo ? tile_lo[mt] : lo;
+          hi = tile_lo[mt] + s_cnt[mt] - 1 > hi ? tile_lo[mt] + s_cnt[mt] - 1 : hi;
+        }
+      pair_lo[pm] = hi < 0 ? 0 : lo;
+      pair_prefix[pm] = acc;
+      acc += hi < 0 ? 0 : hi - lo + 1;
+    }
+    pair_prefix[n_pairs] = acc;
   }
 }
 
-__device__ __forceinline__ void decode_tile(const EstGeom& g, const int* __restrict__ tile_lo,
+__device__ __forceinline__ void decode_tile(int n_groups, const int* __restrict__ tile_lo,
                                             const int* __restrict__ tile_prefix, int tiles_per_head, int tile,
                                             int& bh, int& mt, int& nt) {
   bh = tile / tiles_per_head;
   const int rem = tile - bh * tiles_per_head;
-  int lo = 0, hi = g.n_mtiles;   // find mt with prefix[mt] <= rem < prefix[mt+1]
+  int lo = 0, hi = n_groups;     // find mt with prefix[mt] <= rem < prefix[mt+1]
   while (hi - lo > 1) {
     const int mid = (lo + hi) >> 1;
     if (__ldg(tile_prefix + mid) <= rem) lo = mid; else hi = mid;
@@ -161,7 +177,7 @@ est_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       uint32_t it = 0;
       for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
         int bh, mt, nt;
-        decode_tile(g, tile_lo, tile_prefix, tiles_per_head, tile, bh, mt, nt);
+        decode_tile(g.n_mtiles, tile_lo, tile_prefix, tiles_per_head, tile, bh, mt, nt);
         const int b = bh / g.hq, h = bh - b * g.hq;
         for (int ks = 0; ks < k_steps; ++ks, ++it) {
           const int s = it % kStages;
@@ -215,7 +231,7 @@ est_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     uint32_t local_tile = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local_tile) {
       int bh, mt, nt;
-      decode_tile(g, tile_lo, tile_prefix, tiles_per_head, tile, bh, mt, nt);
+      decode_tile(g.n_mtiles, tile_lo, tile_prefix, tiles_per_head, tile, bh, mt, nt);
       const uint32_t acc = local_tile & 1;
       const uint32_t acc_ph = (local_tile >> 1) & 1;
       const int i = mt * kTileM + r;
@@ -297,6 +313,222 @@ est_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// The same GEMM on CTA PAIRS (thread-block clusters of 2, tcgen05 cta_group::2): a pair computes a 256x256 tile.
+// Each CTA loads its own 128 rows of A and HALF of the tile's 256 columns of B (32 KiB per K step instead of 48),
+// the even CTA issues 256x256x16 MMAs that read both CTAs' shared memory, and each CTA finds the accumulator of
+// its own 128 rows in its own tensor memory, where its four epilogue warps work exactly as in the single-CTA
+// kernel.  The single-CTA kernel is bound by operand bytes in flight per SM (L2 latency x shared-memory
+// capacity); the pair moves a third fewer bytes per FLOP and has six 32 KiB stages in flight.
+//   full[s]   (even CTA)  1 arrival (its producer's expect_tx of both CTAs' bytes) + the bytes of four TMA loads
+//   empty[s]  (each CTA)  1 arrival: the commit of the MMAs that read stage s, delivered to both CTAs
+//   tfull[a]  (each CTA)  1 arrival: the commit of a tile's last MMA, delivered to both CTAs
+//   tempty[a] (even CTA)  8 arrivals: four epilogue warps of each CTA
+constexpr int kPairStages = 6;
+constexpr int kPairBBytes = 128 * kTileK * 2;                // this CTA's half of the B tile: 16 KiB
+constexpr int kPairStageBytes = kABytes + kPairBBytes;       // 32 KiB
+constexpr int kPairSmem = kPairStages * kPairStageBytes + 1024 /*barriers*/ + 1024 /*alignment slack*/;
+
+template <int RBS>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+est_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmKh,
+                     const EstGeom g, const int* __restrict__ pair_lo, const int* __restrict__ pair_prefix,
+                     float* __restrict__ partial, float2* __restrict__ mtile, const uint32_t idesc, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  // the same offset in both CTAs of the pair (the dynamic shared memory of a kernel starts at the same address
+  // in every CTA), which the MMA descriptors rely on
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kPairStages * kPairStageBytes);
+  const uint32_t full0 = smem_u32(bars);                            // [kPairStages]
+  const uint32_t empty0 = smem_u32(bars + kPairStages);             // [kPairStages]
+  const uint32_t tfull0 = smem_u32(bars + 2 * kPairStages);         // [2]
+  const uint32_t tempty0 = smem_u32(bars + 2 * kPairStages + 2);    // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kPairStages + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();                  // 0: issues the MMAs
+  const int pair = blockIdx.x >> 1, n_pairs_grid = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPairStages; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull0 + 8 * a, 1);
+      mbar_init(tempty0 + 8 * a, 8);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmKh);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(tmem_slot), 512);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  cluster_sync_all();               // barriers of both CTAs are initialised before any remote arrival or copy
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int n_groups = (g.n_mtiles + 1) / 2;
+  const int tiles_per_head = __ldg(pair_prefix + n_groups);
+  const int total_tiles = tiles_per_head * g.batch * g.hq;
+  const int k_steps = g.S * g.d_chunks;
+  const int group = g.hq / g.hkv;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (one thread per CTA)
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int tile = pair; tile < total_tiles && !*abort_flag; tile += n_pairs_grid) {
+        int bh, pm, nt;
+        decode_tile(n_groups, pair_lo, pair_prefix, tiles_per_head, tile, bh, pm, nt);
+        const int b = bh / g.hq, h = bh - b * g.hq;
+        const int mt = 2 * pm + static_cast<int>(rank);
+        for (int ks = 0; ks < k_steps; ++ks, ++it) {
+          const int s = it % kPairStages;
+          const uint32_t ph = (it / kPairStages) & 1;
+          if (!mbar_wait(empty0 + 8 * s, ph ^ 1, abort_flag)) break;
+          const int t = ks / g.d_chunks;
+          const int dc = ks - t * g.d_chunks;
+          const uint32_t dstA = smem_u32(smem + s * kPairStageBytes);
+          // all four loads of a stage are counted on the even CTA's barrier
+          const uint32_t full_even = mapa_shared(full0 + 8 * s, 0);
+          if (rank == 0) mbar_expect_tx(full0 + 8 * s, 2 * kPairStageBytes);
+          tma_load_5d_pair(dstA, &tmQ, full_even, dc * kTileK, g.S - 1 - t, mt * kTileM, h, b);
+          tma_load_5d_pair(dstA + kABytes, &tmKh, full_even, dc * kTileK, t, nt * kTileN + static_cast<int>(rank) * 128,
+                           h / group, b);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (one thread of the even CTA)
+    if (lane == 0 && rank == 0) {
+      uint32_t it = 0, local_tile = 0;
+      const uint64_t a_desc0 = smem_desc_sw128(smem_u32(smem), 16, 1024);
+      const uint64_t b_desc0 = smem_desc_sw128(smem_u32(smem) + kABytes, 16, 1024);
+      for (int tile = pair; tile < total_tiles && !*abort_flag; tile += n_pairs_grid, ++local_tile) {
+        const uint32_t acc = local_tile & 1;
+        const uint32_t acc_ph = (local_tile >> 1) & 1;
+        if (!mbar_wait(tempty0 + 8 * acc, acc_ph ^ 1, abort_flag)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * kTileN;
+        bool ok = true;
+        for (int ks = 0; ks < k_steps; ++ks, ++it) {
+          const int s = it % kPairStages;
+          const uint32_t ph = (it / kPairStages) & 1;
+          if (!mbar_wait(full0 + 8 * s, ph, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint64_t a_desc = a_desc0 + static_cast<uint64_t>(s * (kPairStageBytes >> 4));
+          const uint64_t b_desc = b_desc0 + static_cast<uint64_t>(s * (kPairStageBytes >> 4));
+#pragma unroll
+          for (int k4 = 0; k4 < kTileK / 16; ++k4)
+            mma_ss_pair(d_tmem, a_desc + k4 * 2, b_desc + k4 * 2, idesc, (ks > 0 || k4 > 0) ? 1u : 0u);
+          mma_commit_pair(empty0 + 8 * s, 3);  // stage reusable in both CTAs once these MMAs have read it
+        }
+        if (!ok) break;
+        mma_commit_pair(tfull0 + 8 * acc, 3);  // accumulator complete in both CTAs
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (4 warps, thread = tile row)
+    const int quad = warp & 3;                  // TMEM lane quarter this warp may access
+    const int r = quad * 32 + lane;
+    constexpr int kGroups = kTileN / RBS;       // key blocks per tile
+    constexpr int n_chunks = kTileN / 32;
+    uint32_t local_tile = 0;
+    for (int tile = pair; tile < total_tiles; tile += n_pairs_grid, ++local_tile) {
+      int bh, pm, nt;
+      decode_tile(n_groups, pair_lo, pair_prefix, tiles_per_head, tile, bh, pm, nt);
+      const int mt = 2 * pm + static_cast<int>(rank);
+      const uint32_t acc = local_tile & 1;
+      const uint32_t acc_ph = (local_tile >> 1) & 1;
+      const int i = mt * kTileM + r;
+      int lo, hi;
+      row_bounds(g, i < g.rows_total ? i : g.rows_total, lo, hi);   // rows past the end see nothing
+      const int n0 = nt * kTileN;
+      const int clo = lo - n0 > 0 ? lo - n0 : 0;
+      const int chi = hi - n0 < kTileN - 1 ? hi - n0 : kTileN - 1;
+      // warp-uniform: the tensor-memory loads below are warp-collective
+      if (!__all_sync(0xffffffffu, mbar_wait(tfull0 + 8 * acc, acc_ph, abort_flag))) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + acc * kTileN + (static_cast<uint32_t>(quad * 32) << 16);
+      // pass 1: row maximum over the visible columns of this tile
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c8 = 0; c8 < n_chunks; ++c8) {
+        uint32_t v[32];
+        tmem_ld32(taddr + c8 * 32, v);
+        tc_wait_ld();
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+          const int c = c8 * 32 + k;
+          const float x = __uint_as_float(v[k]);
+          if (c >= clo && c <= chi) mx = fmaxf(mx, x);
+        }
+      }
+      const float m_scaled = mx * g.scale_log2;           // scale > 0
+      // pass 2: exp2 and sums over groups of RBS columns
+      const bool row_ok = i < g.rows_total;
+      float* prow = partial + (static_cast<size_t>(bh) * g.rows_total + (row_ok ? i : 0)) * g.kb_total;
+      const int kb0 = nt * kGroups;
+      float tile_sum = 0.f;
+#pragma unroll 1
+      for (int c8 = 0; c8 < n_chunks; ++c8) {
+        uint32_t v[32];
+        tmem_ld32(taddr + c8 * 32, v);
+        tc_wait_ld();
+        if (c8 == n_chunks - 1) {
+          // all TMEM reads of this accumulator are done: hand it back to the MMA thread of the even CTA
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(mapa_shared(tempty0 + 8 * acc, 0));
+        }
+        float gs[32 / RBS];
+#pragma unroll
+        for (int q = 0; q < 32 / RBS; ++q) gs[q] = 0.f;
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+          const int c = c8 * 32 + k;
+          const float x = fmaf(__uint_as_float(v[k]), g.scale_log2, -m_scaled);
+          const float p = (c >= clo && c <= chi) ? fast_exp2(x) : 0.f;
+          gs[k / RBS] += p;
+        }
+#pragma unroll
+        for (int q = 0; q < 32 / RBS; ++q) tile_sum += gs[q];
+        if (row_ok) {
+#pragma unroll
+          for (int q = 0; q < 32 / RBS; ++q) {
+            const int kb = kb0 + c8 * (32 / RBS) + q;
+            if (kb < g.kb_total) prow[kb] = gs[q];
+          }
+        }
+      }
+      if (row_ok)
+        mtile[(static_cast<size_t>(bh) * g.rows_total + i) * g.n_ntiles + nt] = make_float2(m_scaled, tile_sum);
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    // give copies and MMAs still in flight time to land before shared/tensor memory is released
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000) { __nanosleep(1000); }
+    if (threadIdx.x == 0 && status) atomicExch(status, static_cast<int>(kDevWaitTimeout));
+  }
+  // neither CTA may release tensor memory, or leave while the other can still signal its barriers
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, 512);
   }
 }
 
@@ -395,7 +627,7 @@ __global__ void split_f32_kernel(const float* __restrict__ x, int heads, int len
 
 // ------------------------------------------------------------------------------------ host side
 struct EstWorkspace {
-  size_t off_tile_lo, off_tile_prefix, off_rowstat, off_mtile, off_partial, total;
+  size_t off_tile_lo, off_tile_prefix, off_pair_lo, off_pair_prefix, off_rowstat, off_mtile, off_partial, total;
 };
 
 static int fill_geometry(int batch, int hq, int hkv, int q_len, int k_len, int head_dim, int stride, int block_size,
@@ -435,6 +667,8 @@ static EstWorkspace workspace_layout(const EstGeom& g) {
   size_t o = 0;
   w.off_tile_lo = o; o = up(o + sizeof(int) * g.n_mtiles);
   w.off_tile_prefix = o; o = up(o + sizeof(int) * (g.n_mtiles + 1));
+  w.off_pair_lo = o; o = up(o + sizeof(int) * ((g.n_mtiles + 1) / 2));
+  w.off_pair_prefix = o; o = up(o + sizeof(int) * ((g.n_mtiles + 1) / 2 + 1));
   const size_t rows = static_cast<size_t>(g.batch) * g.hq * g.rows_total;
   w.off_rowstat = o; o = up(o + sizeof(float2) * rows);
   w.off_mtile = o; o = up(o + sizeof(float2) * rows * g.n_ntiles);
@@ -470,6 +704,8 @@ int estimate_launch(const void* q, const void* k, int dtype, int batch, int hq, 
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   int* tile_lo = reinterpret_cast<int*>(ws + w.off_tile_lo);
   int* tile_prefix = reinterpret_cast<int*>(ws + w.off_tile_prefix);
+  int* pair_lo = reinterpret_cast<int*>(ws + w.off_pair_lo);
+  int* pair_prefix = reinterpret_cast<int*>(ws + w.off_pair_prefix);
   float2* mtile = reinterpret_cast<float2*>(ws + w.off_mtile);
   float2* rowstat = reinterpret_cast<float2*>(ws + w.off_rowstat);
   float* partial = reinterpret_cast<float*>(ws + w.off_partial);
@@ -491,11 +727,62 @@ int estimate_launch(const void* q, const void* k, int dtype, int batch, int hq, 
     if ((rc = make_tmap_16bit(&tmK, k, 5, dims, str, box))) return rc;
   }
 
-  est_setup_kernel<<<1, 256, sizeof(int) * g.n_mtiles, stream>>>(g, tile_lo, tile_prefix);
+  est_setup_kernel<<<1, 256, sizeof(int) * g.n_mtiles, stream>>>(g, tile_lo, tile_prefix, pair_lo, pair_prefix);
   if ((rc = launch_status())) return rc;
 
+  const int sms = sm_count();
+  // CTA pairs (256x256 tiles) when tiles are 256 columns wide and the two row tiles of a pair see about the
+  // same columns (always, except when a 128-row chunk of the torch branch blanks everything left of it)
+  bool use_pairs = g.tile_n == kTileN && g.n_mtiles >= 2 && (!g.left_blank || g.rcs % (2 * kTileM) == 0);
+#ifdef XB_EST_NO_PAIRS
+  use_pairs = false;
+#endif
+  if (use_pairs) {
+    CUtensorMap tmKh;                     // K with a box of 128 rows: one CTA's half of a 256-column tile
+    {
+      const uint64_t dims[5] = {(uint64_t)head_dim, (uint64_t)stride, (uint64_t)(k_len / stride), (uint64_t)hkv,
+                                (uint64_t)batch};
+      const uint64_t str[4] = {(uint64_t)ksl * 2, (uint64_t)ksl * 2 * stride, (uint64_t)ksh * 2, (uint64_t)ksb * 2};
+      const uint32_t box[5] = {kTileK, 1, 128, 1, 1};
+      if ((rc = make_tmap_16bit(&tmKh, k, 5, dims, str, box))) return rc;
+    }
+    const uint32_t idesc2 = make_idesc_f16(2 * kTileM, kTileN, dtype == XATTN_B200_BF16, false, false);
+    auto launch_pair = [&](auto kern) -> int {
+      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmem) != cudaSuccess)
+        return XATTN_B200_ERR_CUDA;
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(static_cast<unsigned>(sms & ~1), 1, 1);
+      cfg.blockDim = dim3(kGemmThreads, 1, 1);
+      cfg.dynamicSmemBytes = kPairSmem;
+      cfg.stream = stream;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = 2;
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      // every pair must be resident at once (persistent kernel): shrink the grid to what the device can hold
+      int max_clusters = 0;
+      if (cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg) != cudaSuccess || max_clusters < 1)
+        return XATTN_B200_ERR_CUDA;
+      if (static_cast<unsigned>(2 * max_clusters) < cfg.gridDim.x) cfg.gridDim.x = 2 * max_clusters;
+      if (cudaLaunchKernelEx(&cfg, kern, tmQ, tmKh, g, (const int*)pair_lo, (const int*)pair_prefix, partial, mtile,
+                             idesc2, status) != cudaSuccess)
+        return XATTN_B200_ERR_CUDA;
+      return launch_status();
+    };
+    switch (g.rbs) {
+      case 4: rc = launch_pair(est_gemm_pair_kernel<4>); break;
+      case 8: rc = launch_pair(est_gemm_pair_kernel<8>); break;
+      case 16: rc = launch_pair(est_gemm_pair_kernel<16>); break;
+      case 32: rc = launch_pair(est_gemm_pair_kernel<32>); break;
+      default: rc = XATTN_B200_ERR_ARG;
+    }
+    if (rc) return rc;
+  } else {
   const uint32_t idesc = make_idesc_f16(kTileM, g.tile_n, dtype == XATTN_B200_BF16, false, false);
-  const int grid = sm_count();
+  const int grid = sms;
   auto launch = [&](auto kern) -> int {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem) != cudaSuccess)
       return XATTN_B200_ERR_CUDA;
@@ -510,6 +797,7 @@ int estimate_launch(const void* q, const void* k, int dtype, int batch, int hq, 
     default: rc = XATTN_B200_ERR_ARG;
   }
   if (rc) return rc;
+  }
 
   const long long total_rows = static_cast<long long>(batch) * hq * g.rows_total;
   if (total_rows > 0x7fffffffLL || batch * hq > 65535 || g.qb_total > 65535) return XATTN_B200_ERR_LIMIT;
