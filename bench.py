@@ -36,8 +36,8 @@ import torch  # noqa: E402
 METRIC = "prefill_attention_effective_tflops"
 UNIT = "TFLOP/s (dense-equivalent, 4*Lq*Lk*D*Hq/2 causal)"
 # dram__bytes_read.sum + dram__bytes_write.sum of one block_sparse_attn_kernel launch, from the ncu capture that
-# profiles/block_sparse_attn_kernel_llama3_8b_32k.md summarises (406.9 MB + 233.2 MB); other workloads: not captured
-NCU_ATTENTION_TRAFFIC_BYTES = {"llama3_8b_32k": 640_080_640}
+# profiles/block_sparse_attn_kernel_llama3_8b_32k.md summarises (405.6 MB + 233.5 MB); other workloads: not captured
+NCU_ATTENTION_TRAFFIC_BYTES = {"llama3_8b_32k": 639_147_008}
 DEFAULT_WORKLOAD = "llama3_8b_32k"
 
 
@@ -347,7 +347,8 @@ def run_gpu_arm(args):
             e2e=dict(value=e2e_value, unit=UNIT, ms_per_step=ms_e2e, h2d_bytes_per_step=bi, d2h_bytes_per_step=bo,
                      host_cores_bound=len(numa_cores) if numa_cores else None),
             gpu_launches=7 * args.steps,
-            kernels_per_step=["est_setup_kernel", "est_gemm_kernel", "est_rowstat_kernel", "est_blocksum_kernel",
+            kernels_per_step=["est_setup_kernel", "est_gemm_pair_kernel | est_gemm_kernel", "est_rowstat_kernel",
+                              "est_blocksum_kernel",
                               "select_kernel", "block_sparse_attn_kernel<false>", "block_sparse_attn_kernel<true>"],
             phases_ms=dict(estimate=ph[0], select=ph[1], attend=ph[2]),
             block_density=density, roofline=roofline, attention_dense_mask=dense, cpu_baseline=cpu_baseline,

@@ -64,7 +64,8 @@ __host__ __device__ inline void row_bounds(const EstGeom& g, int i, int& lo, int
 // tile_lo[mt], tile_prefix[mt] (exclusive prefix of tile counts, n_mtiles+1 entries)
 __global__ void est_setup_kernel(EstGeom g, int* __restrict__ tile_lo, int* __restrict__ tile_prefix,
                                  int* __restrict__ pair_lo, int* __restrict__ pair_prefix) {
-  extern __shared__ int s_cnt[];
+  extern __shared__ int s_cnt[];                  // [n_mtiles] tile counts, then [n_mtiles] first tiles
+  int* s_lo = s_cnt + g.n_mtiles;
   for (int mt = threadIdx.x; mt < g.n_mtiles; mt += blockDim.x) {
     // lo(i) and hi(i) never decrease with i, so the tile's column range is [lo(first row), hi(last valid row)]
     const int i0 = mt * kTileM;
@@ -78,12 +79,13 @@ __global__ void est_setup_kernel(EstGeom g, int* __restrict__ tile_lo, int* __re
       row_bounds(g, i1 - 1, lo, hi_max);
     }
     if (hi_max < lo_min) {
-      tile_lo[mt] = 0;
+      s_lo[mt] = 0;
       s_cnt[mt] = 0;
     } else {
-      tile_lo[mt] = lo_min / g.tile_n;
+      s_lo[mt] = lo_min / g.tile_n;
       s_cnt[mt] = hi_max / g.tile_n - lo_min / g.tile_n + 1;
     }
+    tile_lo[mt] = s_lo[mt];
   }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -100,8 +102,8 @@ __global__ void est_setup_kernel(EstGeom g, int* __restrict__ tile_lo, int* __re
       int lo = 0x7fffffff, hi = -1;
       for (int mt = 2 * pm; mt < 2 * pm + 2 && mt < g.n_mtiles; ++mt)
         if (s_cnt[mt] > 0) {
-          lo = tile_lo[mt] < lo ? tile_lo[mt] : lo;
-          hi = tile_lo[mt] + s_cnt[mt] - 1 > hi ? tile_lo[mt] + s_cnt[mt] - 1 : hi;
+          lo = s_lo[mt] < lo ? s_lo[mt] : lo;
+          hi = s_lo[mt] + s_cnt[mt] - 1 > hi ? s_lo[mt] + s_cnt[mt] - 1 : hi;
         }
       pair_lo[pm] = hi < 0 ? 0 : lo;
       pair_prefix[pm] = acc;
@@ -727,7 +729,7 @@ int estimate_launch(const void* q, const void* k, int dtype, int batch, int hq, 
     if ((rc = make_tmap_16bit(&tmK, k, 5, dims, str, box))) return rc;
   }
 
-  est_setup_kernel<<<1, 256, sizeof(int) * g.n_mtiles, stream>>>(g, tile_lo, tile_prefix, pair_lo, pair_prefix);
+  est_setup_kernel<<<1, 256, 2 * sizeof(int) * g.n_mtiles, stream>>>(g, tile_lo, tile_prefix, pair_lo, pair_prefix);
   if ((rc = launch_status())) return rc;
 
   const int sms = sm_count();
