@@ -127,6 +127,88 @@ __device__ __forceinline__ void decode_tile(int n_groups, const int* __restrict_
   nt = __ldg(tile_lo + mt) + rem - __ldg(tile_prefix + mt);
 }
 
+// Epilogue of one accumulator tile for one row (thread): softmax statistics and un-normalised block sums of the
+// tile's visible columns [clo, chi].  Two passes over the row in tensor memory (maximum, then exp2 and sums over
+// groups of RBS columns), the load of the next 32 columns in flight while the current ones are processed; chunks
+// that every lane of the warp sees completely skip the per-element range test.  `release` is called once all
+// tensor-memory reads of the tile are done.
+template <int RBS, typename Release>
+__device__ __forceinline__ void est_epilogue_row(const EstGeom& g, uint32_t taddr, int n_chunks, int clo, int chi,
+                                                 bool row_ok, float* __restrict__ prow, int kb0,
+                                                 float2* __restrict__ mslot, Release release) {
+  auto fully_visible = [&](int c8) { return __all_sync(0xffffffffu, clo <= c8 * 32 && chi >= c8 * 32 + 31); };
+  // pass 1: row maximum over the visible columns
+  float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+  {
+    auto max_chunk = [&](const uint32_t (&v)[32], int c8) {
+      if (fully_visible(c8)) {
+#pragma unroll
+        for (int k = 0; k < 32; ++k) mx4[k & 3] = fmaxf(mx4[k & 3], __uint_as_float(v[k]));
+      } else {
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+          const int c = c8 * 32 + k;
+          if (c >= clo && c <= chi) mx4[k & 3] = fmaxf(mx4[k & 3], __uint_as_float(v[k]));
+        }
+      }
+    };
+    uint32_t va[32], vb[32];
+    tmem_ld32(taddr, va);
+#pragma unroll 1
+    for (int c8 = 0; c8 < n_chunks; c8 += 2) {
+      tc_wait_ld();
+      tmem_ld32(taddr + (c8 + 1) * 32, vb);
+      max_chunk(va, c8);
+      tc_wait_ld();
+      if (c8 + 2 < n_chunks) tmem_ld32(taddr + (c8 + 2) * 32, va);
+      max_chunk(vb, c8 + 1);
+    }
+  }
+  const float m_scaled = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * g.scale_log2;     // scale > 0
+  // pass 2: exp2 and sums over groups of RBS columns
+  float tile_sum = 0.f;
+  {
+    auto sum_chunk = [&](const uint32_t (&v)[32], int c8) {
+      float gs[32 / RBS];
+#pragma unroll
+      for (int q = 0; q < 32 / RBS; ++q) gs[q] = 0.f;
+      if (fully_visible(c8)) {
+#pragma unroll
+        for (int k = 0; k < 32; ++k) gs[k / RBS] += fast_exp2(fmaf(__uint_as_float(v[k]), g.scale_log2, -m_scaled));
+      } else {
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+          const int c = c8 * 32 + k;
+          const float x = fmaf(__uint_as_float(v[k]), g.scale_log2, -m_scaled);
+          gs[k / RBS] += (c >= clo && c <= chi) ? fast_exp2(x) : 0.f;
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < 32 / RBS; ++q) tile_sum += gs[q];
+      if (row_ok) {
+#pragma unroll
+        for (int q = 0; q < 32 / RBS; ++q) {
+          const int kb = kb0 + c8 * (32 / RBS) + q;
+          if (kb < g.kb_total) prow[kb] = gs[q];
+        }
+      }
+    };
+    uint32_t va[32], vb[32];
+    tmem_ld32(taddr, va);
+#pragma unroll 1
+    for (int c8 = 0; c8 < n_chunks; c8 += 2) {
+      tc_wait_ld();
+      tmem_ld32(taddr + (c8 + 1) * 32, vb);
+      sum_chunk(va, c8);
+      tc_wait_ld();
+      if (c8 + 2 < n_chunks) tmem_ld32(taddr + (c8 + 2) * 32, va);
+      else release();                                   // the tile's last load has completed
+      sum_chunk(vb, c8 + 1);
+    }
+  }
+  if (row_ok) *mslot = make_float2(m_scaled, tile_sum);
+}
+
 template <int RBS>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 est_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const EstGeom g,
@@ -246,59 +328,15 @@ est_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (!__all_sync(0xffffffffu, mbar_wait(tfull0 + 8 * acc, acc_ph, abort_flag))) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * kTileN + (static_cast<uint32_t>(quad * 32) << 16);
-      // pass 1: row maximum over the visible columns of this tile
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c8 = 0; c8 < n_chunks; ++c8) {
-        uint32_t v[32];
-        tmem_ld32(taddr + c8 * 32, v);
-        tc_wait_ld();
-#pragma unroll
-        for (int k = 0; k < 32; ++k) {
-          const int c = c8 * 32 + k;
-          const float x = __uint_as_float(v[k]);
-          if (c >= clo && c <= chi) mx = fmaxf(mx, x);
-        }
-      }
-      const float m_scaled = mx * g.scale_log2;           // scale > 0
-      // pass 2: exp2 and sums over groups of RBS columns
       const bool row_ok = i < g.rows_total;
-      float* prow = partial + (static_cast<size_t>(bh) * g.rows_total + (row_ok ? i : 0)) * g.kb_total;
-      const int kb0 = nt * kGroups;
-      float tile_sum = 0.f;
-#pragma unroll 1
-      for (int c8 = 0; c8 < n_chunks; ++c8) {
-        uint32_t v[32];
-        tmem_ld32(taddr + c8 * 32, v);
-        tc_wait_ld();
-        if (c8 == n_chunks - 1) {
-          // all TMEM reads of this accumulator are done: hand it back to the MMA thread
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(tempty0 + 8 * acc);
-        }
-        float gs[32 / RBS];
-#pragma unroll
-        for (int q = 0; q < 32 / RBS; ++q) gs[q] = 0.f;
-#pragma unroll
-        for (int k = 0; k < 32; ++k) {
-          const int c = c8 * 32 + k;
-          const float x = fmaf(__uint_as_float(v[k]), g.scale_log2, -m_scaled);
-          const float p = (c >= clo && c <= chi) ? fast_exp2(x) : 0.f;
-          gs[k / RBS] += p;
-        }
-#pragma unroll
-        for (int q = 0; q < 32 / RBS; ++q) tile_sum += gs[q];
-        if (row_ok) {
-#pragma unroll
-          for (int q = 0; q < 32 / RBS; ++q) {
-            const int kb = kb0 + c8 * (32 / RBS) + q;
-            if (kb < g.kb_total) prow[kb] = gs[q];
-          }
-        }
-      }
-      if (row_ok)
-        mtile[(static_cast<size_t>(bh) * g.rows_total + i) * g.n_ntiles + nt] = make_float2(m_scaled, tile_sum);
+      const size_t rrow = static_cast<size_t>(bh) * g.rows_total + (row_ok ? i : 0);
+      est_epilogue_row<RBS>(g, taddr, n_chunks, clo, chi, row_ok, partial + rrow * g.kb_total, nt * kGroups,
+                            mtile + rrow * g.n_ntiles + nt, [&]() {
+                              // all TMEM reads of this accumulator are done: hand it back to the MMA thread
+                              tc_fence_before();
+                              __syncwarp();
+                              if (lane == 0) mbar_arrive(tempty0 + 8 * acc);
+                            });
     }
   }
 
@@ -461,59 +499,16 @@ est_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       if (!__all_sync(0xffffffffu, mbar_wait(tfull0 + 8 * acc, acc_ph, abort_flag))) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * kTileN + (static_cast<uint32_t>(quad * 32) << 16);
-      // pass 1: row maximum over the visible columns of this tile
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c8 = 0; c8 < n_chunks; ++c8) {
-        uint32_t v[32];
-        tmem_ld32(taddr + c8 * 32, v);
-        tc_wait_ld();
-#pragma unroll
-        for (int k = 0; k < 32; ++k) {
-          const int c = c8 * 32 + k;
-          const float x = __uint_as_float(v[k]);
-          if (c >= clo && c <= chi) mx = fmaxf(mx, x);
-        }
-      }
-      const float m_scaled = mx * g.scale_log2;           // scale > 0
-      // pass 2: exp2 and sums over groups of RBS columns
       const bool row_ok = i < g.rows_total;
-      float* prow = partial + (static_cast<size_t>(bh) * g.rows_total + (row_ok ? i : 0)) * g.kb_total;
-      const int kb0 = nt * kGroups;
-      float tile_sum = 0.f;
-#pragma unroll 1
-      for (int c8 = 0; c8 < n_chunks; ++c8) {
-        uint32_t v[32];
-        tmem_ld32(taddr + c8 * 32, v);
-        tc_wait_ld();
-        if (c8 == n_chunks - 1) {
-          // all TMEM reads of this accumulator are done: hand it back to the MMA thread of the even CTA
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(mapa_shared(tempty0 + 8 * acc, 0));
-        }
-        float gs[32 / RBS];
-#pragma unroll
-        for (int q = 0; q < 32 / RBS; ++q) gs[q] = 0.f;
-#pragma unroll
-        for (int k = 0; k < 32; ++k) {
-          const int c = c8 * 32 + k;
-          const float x = fmaf(__uint_as_float(v[k]), g.scale_log2, -m_scaled);
-          const float p = (c >= clo && c <= chi) ? fast_exp2(x) : 0.f;
-          gs[k / RBS] += p;
-        }
-#pragma unroll
-        for (int q = 0; q < 32 / RBS; ++q) tile_sum += gs[q];
-        if (row_ok) {
-#pragma unroll
-          for (int q = 0; q < 32 / RBS; ++q) {
-            const int kb = kb0 + c8 * (32 / RBS) + q;
-            if (kb < g.kb_total) prow[kb] = gs[q];
-          }
-        }
-      }
-      if (row_ok)
-        mtile[(static_cast<size_t>(bh) * g.rows_total + i) * g.n_ntiles + nt] = make_float2(m_scaled, tile_sum);
+      const size_t rrow = static_cast<size_t>(bh) * g.rows_total + (row_ok ? i : 0);
+      est_epilogue_row<RBS>(g, taddr, n_chunks, clo, chi, row_ok, partial + rrow * g.kb_total, nt * kGroups,
+                            mtile + rrow * g.n_ntiles + nt, [&]() {
+                              // all TMEM reads of this accumulator are done: hand it back to the MMA thread of
+                              // the even CTA
+                              tc_fence_before();
+                              __syncwarp();
+                              if (lane == 0) mbar_arrive_cluster(mapa_shared(tempty0 + 8 * acc, 0));
+                            });
     }
   }
 
