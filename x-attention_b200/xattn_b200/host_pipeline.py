@@ -66,12 +66,13 @@ def Xattention_prefill_host(query_states: torch.Tensor, key_states: torch.Tensor
                             stride, norm=1, threshold: Union[float, torch.Tensor] = 0.8, block_size=128,
                             causal=True, chunk_size=None, keep_sink=False, keep_recent=False,
                             device: Optional[torch.device] = None, out: Optional[torch.Tensor] = None,
-                            groups_per_step: int = 1) -> torch.Tensor:
+                            groups_per_step: int = 1, q_splits: int = 2) -> torch.Tensor:
     """Same computation as Xattention_prefill (xattn/src/Xattention.py:302-402) for host tensors.
 
     query_states [1,Hq,L,D], key/value_states [1,Hkv,L,D] on the CPU (pin them: pageable memory makes the
     copies synchronous).  Returns a pinned CPU tensor [1,Hq,L,D] (contiguous), or fills `out`.  The call
-    returns when the result is complete."""
+    returns when the result is complete.  `groups_per_step` kv groups are resident at a time; the query heads of
+    a group slice run in `q_splits` steps (when that divides them)."""
     assert block_size == 128
     B, Hq, Lq, D = query_states.shape
     assert B == 1
@@ -86,40 +87,66 @@ def Xattention_prefill_host(query_states: torch.Tensor, key_states: torch.Tensor
         out = torch.empty(1, Hq, Lq, D, dtype=cdtype).pin_memory()
     g = ops.geometry(Lq, Lk, chunk_size, stride, block_size)
     slices = group_slices(Hq, Hkv, groups_per_step)
-    nq = slices[0][1] - slices[0][0]
     nk = slices[0][3] - slices[0][2]
+    # a step = a slice of the query heads of one kv-group slice; its K/V are copied with the first step only.
+    # Smaller steps shorten what cannot overlap: the first step's input copy and the last step's output copy.
+    steps = []
+    for (q0, q1, k0, k1) in slices:
+        n = q1 - q0
+        # (only for a single kv head per slice: the kernels map local query head h to kv head h // (n / kv heads))
+        parts = q_splits if (q_splits > 0 and k1 - k0 == 1 and n % q_splits == 0) else 1
+        for j in range(parts):
+            steps.append((q0 + j * (n // parts), q0 + (j + 1) * (n // parts), k0, k1, j == 0, j == parts - 1))
+    nq = max(st[1] - st[0] for st in steps)
     with torch.cuda.device(dev):
         h2d, d2h = _streams(dev)
         compute = torch.cuda.current_stream(dev)
-        bufs = []
+        qo, kv = [], []
         for _ in range(2):
-            bufs.append(dict(
+            qo.append(dict(
                 q=torch.empty(1, nq, Lq, D, dtype=query_states.dtype, device=dev),
-                k=torch.empty(1, nk, Lk, D, dtype=key_states.dtype, device=dev),
-                v=torch.empty(1, nk, Lk, D, dtype=value_states.dtype, device=dev),
                 o=torch.empty(1, nq, Lq, D, dtype=cdtype, device=dev),
                 loaded=torch.cuda.Event(), computed=torch.cuda.Event(), stored=torch.cuda.Event(), used=False))
+            kv.append(dict(
+                k=torch.empty(1, nk, Lk, D, dtype=key_states.dtype, device=dev),
+                v=torch.empty(1, nk, Lk, D, dtype=value_states.dtype, device=dev),
+                loaded_k=torch.cuda.Event(), loaded_v=torch.cuda.Event(), released=torch.cuda.Event(), used=False))
         h2d.wait_stream(compute)
-        for i, (q0, q1, k0, k1) in enumerate(slices):
-            b = bufs[i & 1]
+        group_no = -1
+        for i, (q0, q1, k0, k1, first, last) in enumerate(steps):
+            if first:
+                group_no += 1
+            b, c = qo[i & 1], kv[group_no & 1]
             hq_n, hk_n = q1 - q0, k1 - k0
             with torch.cuda.stream(h2d):
                 if b["used"]:
-                    h2d.wait_event(b["computed"])          # inputs of step i-2 no longer needed
+                    h2d.wait_event(b["computed"])          # q of step i-2 no longer needed
                 b["q"][:, :hq_n].copy_(query_states[:, q0:q1], non_blocking=True)
-                b["k"][:, :hk_n].copy_(key_states[:, k0:k1], non_blocking=True)
-                b["v"][:, :hk_n].copy_(value_states[:, k0:k1], non_blocking=True)
-                b["loaded"].record(h2d)
+                if first:
+                    if c["used"]:
+                        h2d.wait_event(c["released"])      # K/V of the group two back no longer needed
+                    c["k"][:, :hk_n].copy_(key_states[:, k0:k1], non_blocking=True)
+                    c["loaded_k"].record(h2d)
+                    b["loaded"].record(h2d)
+                    c["v"][:, :hk_n].copy_(value_states[:, k0:k1], non_blocking=True)   # not needed by the estimate
+                    c["loaded_v"].record(h2d)
+                else:
+                    b["loaded"].record(h2d)
             compute.wait_event(b["loaded"])
-            if b["used"]:
-                compute.wait_event(b["stored"])            # output buffer of step i-2 has left the device
+            compute.wait_event(c["loaded_k"])
             thr = threshold[q0:q1] if isinstance(threshold, torch.Tensor) else threshold
-            qd, kd, vd = b["q"][:, :hq_n], b["k"][:, :hk_n], b["v"][:, :hk_n]
+            qd, kd, vd = b["q"][:, :hq_n], c["k"][:, :hk_n], c["v"][:, :hk_n]
             sums = ops.estimate_block_sums(qd, kd, stride, block_size, chunk_size, float(norm), bool(causal))
             _, idx, cnt = ops.select_blocks(sums, g["bpc"], g["block_offset"], thr, bool(causal), True,
                                             bool(keep_sink), bool(keep_recent), list_shape=(Lq, Lk), want_mask=False)
+            compute.wait_event(c["loaded_v"])
+            if b["used"]:
+                compute.wait_event(b["stored"])            # output buffer of step i-2 has left the device
             ops.block_sparse_attention(qd, kd, vd, idx, cnt, bool(causal), out=b["o"][:, :hq_n])
             b["computed"].record(compute)
+            if last:
+                c["released"].record(compute)
+                c["used"] = True
             with torch.cuda.stream(d2h):
                 d2h.wait_event(b["computed"])
                 out[:, q0:q1].copy_(b["o"][:, :hq_n], non_blocking=True)
