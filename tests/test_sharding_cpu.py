@@ -126,3 +126,26 @@ def test_sharded_equals_unsharded_gloo(hq, hkv, world):
     mp.spawn(_worker, args=(world, port, hq, hkv, ret), nprocs=world, join=True)
     assert len(ret) == world
     assert all(err == 0.0 for err in ret.values()), dict(ret)
+
+
+def test_host_pipeline_steps_keep_the_kv_head_mapping():
+    """Every step of the host pipeline must map its local query heads to the right kv heads with the rule the
+    kernels apply (local q head h -> local kv head h // (n_q / n_kv)), cover every head once, in order, and
+    copy K/V exactly once per slice."""
+    from xattn_b200.host_pipeline import plan_steps
+    for hq, hkv in ((32, 8), (12, 3), (28, 4), (24, 24), (8, 1), (6, 2)):
+        rep = hq // hkv
+        for gps in (1, 2, 3):
+            for splits in (0, 1, 2, 4):
+                steps = plan_steps(hq, hkv, gps, splits)
+                seen = []
+                firsts = 0
+                for (q0, q1, k0, k1, first, last) in steps:
+                    nq, nk = q1 - q0, k1 - k0
+                    assert nq > 0 and nk > 0 and nq % nk == 0
+                    for h in range(nq):
+                        assert k0 + h // (nq // nk) == (q0 + h) // rep, (hq, hkv, gps, splits, q0, h)
+                    seen.extend(range(q0, q1))
+                    firsts += int(first)
+                assert seen == list(range(hq))
+                assert firsts == (hkv + gps - 1) // gps

@@ -22,11 +22,13 @@
 //
 // Lists are walked from the last entry (the diagonal block when causal, which usually holds the row
 // maximum) to the first, so the running maximum settles at the first block and O is rarely rescaled.
-// Inside a stream every 128-key block is processed as two 64-key halves: S of half h goes to its own
-// 64-column TMEM buffer, so while the softmax warpgroup works on one half the tensor pipe computes the other
-// half's S (and the previous half's P.V).  K and V reach shared memory as four 16 KiB half-tiles per block.
-// TMEM columns: [0,128) S of stream 0 (two 64-column halves), [128,256) S of stream 1, [256,384) O of stream 0,
-// [384,512) O of stream 1.
+// The kernel is a template over how a stream walks a 128-key block (see kHalfModeMinBlocks): as one block
+// (K and V as 32 KiB tiles, whole-block softmax: the shortest chain per item, for short lists), or as two
+// 64-key halves (S of half h in its own 64-column TMEM buffer, so while the softmax warpgroup works on one half
+// the tensor pipe computes the other half's S and the previous half's P.V; K and V as four 16 KiB half-tiles
+// per block: for long lists).  Both instantiations are launched; each CTA works in one of them.
+// TMEM columns: [0,128) S of stream 0 (two 64-column halves in half mode), [128,256) S of stream 1,
+// [256,384) O of stream 0, [384,512) O of stream 1.
 #include <math.h>
 
 #include "host_common.cuh"

@@ -62,6 +62,20 @@ def group_slices(hq: int, hkv: int, groups_per_step: int = 1):
     return out
 
 
+def plan_steps(hq: int, hkv: int, groups_per_step: int = 1, q_splits: int = 2):
+    """Steps of the host pipeline: [(q0, q1, k0, k1, first_of_slice, last_of_slice)].  A slice is `groups_per_step`
+    whole kv groups (its K/V are copied with its first step); the query heads of a slice that holds ONE kv head
+    run in `q_splits` steps when that divides them.  A slice with several kv heads is never split: the kernels
+    map local query head h to local kv head h // (query heads / kv heads), which a partial slice would break."""
+    steps = []
+    for (q0, q1, k0, k1) in group_slices(hq, hkv, groups_per_step):
+        n = q1 - q0
+        parts = q_splits if (q_splits > 0 and k1 - k0 == 1 and n % q_splits == 0) else 1
+        for j in range(parts):
+            steps.append((q0 + j * (n // parts), q0 + (j + 1) * (n // parts), k0, k1, j == 0, j == parts - 1))
+    return steps
+
+
 def Xattention_prefill_host(query_states: torch.Tensor, key_states: torch.Tensor, value_states: torch.Tensor,
                             stride, norm=1, threshold: Union[float, torch.Tensor] = 0.8, block_size=128,
                             causal=True, chunk_size=None, keep_sink=False, keep_recent=False,
@@ -88,15 +102,8 @@ def Xattention_prefill_host(query_states: torch.Tensor, key_states: torch.Tensor
     g = ops.geometry(Lq, Lk, chunk_size, stride, block_size)
     slices = group_slices(Hq, Hkv, groups_per_step)
     nk = slices[0][3] - slices[0][2]
-    # a step = a slice of the query heads of one kv-group slice; its K/V are copied with the first step only.
-    # Smaller steps shorten what cannot overlap: the first step's input copy and the last step's output copy.
-    steps = []
-    for (q0, q1, k0, k1) in slices:
-        n = q1 - q0
-        # (only for a single kv head per slice: the kernels map local query head h to kv head h // (n / kv heads))
-        parts = q_splits if (q_splits > 0 and k1 - k0 == 1 and n % q_splits == 0) else 1
-        for j in range(parts):
-            steps.append((q0 + j * (n // parts), q0 + (j + 1) * (n // parts), k0, k1, j == 0, j == parts - 1))
+    # smaller steps shorten what cannot overlap: the first step's input copy and the last step's output copy
+    steps = plan_steps(Hq, Hkv, groups_per_step, q_splits)
     nq = max(st[1] - st[0] for st in steps)
     with torch.cuda.device(dev):
         h2d, d2h = _streams(dev)
