@@ -34,24 +34,28 @@ struct SelParams {
   int list_q_blocks, list_k_blocks, list_q_len, list_k_len;
   int np2;            // k_blocks rounded up to a power of two (>= 32)
   int warps_per_cta;
-  int vals_bytes, keys_bytes, per_warp_bytes;   // keys: one sort buffer per CTA, taken in turn by its warps
+  int words;          // 32-column words per row
+  int vals_bytes, idx_bytes, keys_bytes, per_warp_bytes;   // keys: one sort buffer per CTA, taken in turn by its warps
   int rows_total;
+  int vec4;           // rows can be read as float4 / masks written as 16-byte vectors
 };
-
-__device__ __forceinline__ bool list_keeps(int causal, int R, int j, int list_q_len, int list_k_len) {
-  if (!causal) return true;
-  // last token of query block R sees keys up to this position (query end aligned to key end)
-  int last_q = R * 128 + 127;
-  if (last_q > list_q_len - 1) last_q = list_q_len - 1;
-  return static_cast<long long>(j) * 128 <= static_cast<long long>(last_q) + (list_k_len - list_q_len);
-}
 
 __device__ __forceinline__ double warp_sum(double v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   return v;
 }
+// bits of 32-column word t whose column is <= hi
+__device__ __forceinline__ uint32_t bits_le(int hi, int t) {
+  const int r = hi - 32 * t;
+  return r < 0 ? 0u : (r >= 31 ? 0xffffffffu : (2u << r) - 1u);
+}
 
+// One warp per row.  The row is read once (16-byte loads): fp64 total, the forced blocks, and the positive
+// scores compacted in column order into shared memory (score rows are sparse: most blocks hold no mass).
+// Zero-score columns are not stored: all of them rank after the positive ones, in column order, and the rule
+// can only take the first of them or all of them (see below).  Taken columns are a bitmap, so the mask row and
+// the ascending block list are produced word by word.
 __global__ void select_kernel(const float* __restrict__ sums, const SelParams p,
                               const float* __restrict__ thr_per_head, uint8_t* __restrict__ mask_out,
                               int32_t* __restrict__ idx_out, int32_t* __restrict__ cnt_out, int* status) {
@@ -65,14 +69,18 @@ __global__ void select_kernel(const float* __restrict__ sums, const SelParams p,
   if (w >= p.rows_total) return;                         // whole warps leave; no block-wide barrier below
   unsigned long long* keys = reinterpret_cast<unsigned long long*>(sel_smem);        // [np2], shared by the CTA
   uint8_t* base_ptr = sel_smem + p.keys_bytes + static_cast<size_t>(wib) * p.per_warp_bytes;
-  float* vals = reinterpret_cast<float*>(base_ptr);                                  // [N]  (-1 = removed)
-  uint8_t* mrow = base_ptr + p.vals_bytes;                                           // [N]
+  float* cval = reinterpret_cast<float*>(base_ptr);                                  // [M] positive scores (-1 = taken)
+  uint16_t* cidx = reinterpret_cast<uint16_t*>(base_ptr + p.vals_bytes);             // [M] their columns, ascending
+  uint32_t* taken = reinterpret_cast<uint32_t*>(base_ptr + p.vals_bytes + p.idx_bytes);   // [words]
+  uint32_t* cand = taken + p.words;                                                  // [words] columns with a positive score
 
   const int bh = w / p.q_blocks;
   const int R = w - bh * p.q_blocks;
   const int h = bh % p.heads;
   const int N = p.k_blocks;
+  const int W = p.words;
   const float* x = sums + static_cast<size_t>(w) * N;
+  auto valid = [&](int t) -> uint32_t { return bits_le(N - 1, t); };
 
   const int cur = p.block_offset + (R / p.bpc) * p.bpc;
   const int d = cur + R % p.bpc;
@@ -81,57 +89,122 @@ __global__ void select_kernel(const float* __restrict__ sums, const SelParams p,
   const int lag = n_forced == 1 ? 1 : 0;
   const int n_others = N - n_forced;
 
+  for (int t = lane; t < W; t += 32) { taken[t] = 0u; cand[t] = 0u; }
+  __syncwarp();
+
+  // ---- the row, once
   double part = 0.0, fpart = 0.0;
-  for (int j = lane; j < N; j += 32) {
-    const float v = x[j];
-    part += static_cast<double>(v);
-    const bool forced = p.causal && (j == d || (f0 && j == 0));
-    if (forced) fpart += static_cast<double>(v);
-    vals[j] = forced ? -1.f : (v > 0.f ? v : 0.f);
-    mrow[j] = forced ? 1 : 0;
+  int M = 0;                                       // positive non-forced scores so far (warp-uniform)
+  // 1024 columns at a time: all loads of the piece are issued before any of it is processed, so a row costs one
+  // memory round trip per 1024 columns instead of one per 128
+  for (int j1 = 0; j1 < N; j1 += 1024) {
+    float vv[8][4];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int j = j1 + u * 128 + 4 * lane;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) vv[u][e] = 0.f;
+      if (p.vec4) {
+        if (j < N) {
+          const float4 q = __ldg(reinterpret_cast<const float4*>(x + j));
+          vv[u][0] = q.x; vv[u][1] = q.y; vv[u][2] = q.z; vv[u][3] = q.w;
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (j + e < N) vv[u][e] = __ldg(x + j + e);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int j0 = j1 + u * 128;
+      if (j0 >= N) break;
+      const int j = j0 + 4 * lane;
+      const float (&v)[4] = vv[u];
+      uint32_t nib = 0u;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int jj = j + e;
+        if (jj < N) {
+          part += static_cast<double>(v[e]);
+          const bool forced = p.causal && (jj == d || (f0 && jj == 0));
+          if (forced) fpart += static_cast<double>(v[e]);
+          else if (v[e] > 0.f) nib |= 1u << e;
+        }
+      }
+      // candidate bitmap: eight lanes share a word
+      uint32_t word = nib << (4 * (lane & 7));
+      word |= __shfl_xor_sync(0xffffffffu, word, 1);
+      word |= __shfl_xor_sync(0xffffffffu, word, 2);
+      word |= __shfl_xor_sync(0xffffffffu, word, 4);
+      const int wi = (j0 >> 5) + (lane >> 3);
+      if ((lane & 7) == 0 && wi < W) cand[wi] = word;
+      // compaction in column order (rows are sparse: skip the scan when the piece holds no positive score)
+      if (__any_sync(0xffffffffu, nib != 0u)) {
+        const int c = __popc(nib);
+        int incl = c;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int up = __shfl_up_sync(0xffffffffu, incl, o);
+          if (lane >= o) incl += up;
+        }
+        int pos = M + incl - c;
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if ((nib >> e) & 1u) {
+            cval[pos] = v[e];
+            cidx[pos] = static_cast<uint16_t>(j + e);
+            ++pos;
+          }
+        M += __shfl_sync(0xffffffffu, incl, 31);
+      }
+    }
   }
   const double total = warp_sum(part);
   const double fsum = warp_sum(fpart);
   const double thr = thr_per_head ? static_cast<double>(thr_per_head[h]) : p.threshold;
   const double req = total * thr;
+  if (lane == 0 && p.causal) {
+    taken[d >> 5] |= 1u << (d & 31);
+    if (f0) taken[0] |= 1u;
+  }
   __syncwarp();
 
   bool untaken = !(req > 0.0);                     // the leading slots of the reference compare 0 < req too
   if (req > 0.0) {
     int i = 1;                                     // rank being decided
+    int live = M;                                  // positive scores not ranked yet
     double s_cur = 0.0, s_lag = 0.0;               // prefix[i-1], prefix[max(i-2,0)] of the ranked scores
-    bool sort_rest = false;
-    while (i <= n_others) {
+    bool stop = false;                             // a rank was refused: every later rank is refused too
+    // ---- ranks that hold a positive score: the largest remaining one (lowest column on ties) at a time
+    while (live > 0 && i <= kPeelMax) {
       const double c = lag ? (i == 1 ? 0.0 : fsum + s_lag) : fsum + s_cur;
-      if (!(c < req)) { untaken = true; break; }
-      if (i > kPeelMax) { sort_rest = true; break; }
-      // largest remaining score, lowest index on ties
+      if (!(c < req)) { untaken = true; stop = true; break; }
       float bv = -1.f;
-      int bj = 0x7fffffff;
-      for (int j = lane; j < N; j += 32) {
-        const float v = vals[j];
-        if (v > bv) { bv = v; bj = j; }
+      int bp = 0x7fffffff;
+      for (int t = lane; t < M; t += 32) {
+        const float v = cval[t];
+        if (v > bv) { bv = v; bp = t; }
       }
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) {
         const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-        const int oj = __shfl_xor_sync(0xffffffffu, bj, o);
-        if (ov > bv || (ov == bv && oj < bj)) { bv = ov; bj = oj; }
+        const int op = __shfl_xor_sync(0xffffffffu, bp, o);
+        if (ov > bv || (ov == bv && op < bp)) { bv = ov; bp = op; }
       }
-      if (bv == 0.f && fsum + s_cur < req) {
-        // only zero scores are left and the prefix no longer moves: every remaining rank is taken
-        for (int j = lane; j < N; j += 32)
-          if (vals[j] == 0.f) mrow[j] = 1;
-        i = n_others + 1;
-        break;
+      if (lane == 0) {
+        const int col = cidx[bp];
+        cval[bp] = -1.f;
+        taken[col >> 5] |= 1u << (col & 31);
       }
-      if (lane == (bj & 31)) { vals[bj] = -1.f; mrow[bj] = 1; }
       __syncwarp();
       s_lag = s_cur;
       s_cur += static_cast<double>(bv);
       ++i;
+      --live;
     }
-    if (sort_rest) {
+    // ---- flat rows: sort what is left of the positive scores, fp64 prefix, decide per rank
+    if (!stop && live > 0) {
       // the sort buffer is shared by the warps of the CTA (flat rows are the exception): take it in turn.
       // The holder always releases it after a bounded amount of work; the spin itself is bounded too.
       int got = 0;
@@ -146,90 +219,168 @@ __global__ void select_kernel(const float* __restrict__ sums, const SelParams p,
       if (!got) {
         if (lane == 0 && status) atomicExch(status, 101);
         untaken = true;
-        sort_rest = false;
-      }
-    }
-    if (sort_rest) {
-      // ranks i.. : sort what is left (descending score, ascending index), fp64 prefix, decide per rank
-      for (int t = lane; t < p.np2; t += 32) {
-        unsigned long long key = 0ull;
-        if (t < N && vals[t] >= 0.f)
-          key = (static_cast<unsigned long long>(__float_as_uint(vals[t])) << 32) | (0xFFFFFFFFull - static_cast<unsigned>(t));
-        keys[t] = key;
-      }
-      __syncwarp();
-      for (int k = 2; k <= p.np2; k <<= 1) {
-        for (int j = k >> 1; j > 0; j >>= 1) {
-          for (int t = lane; t < p.np2; t += 32) {
-            const int ixj = t ^ j;
-            if (ixj > t) {
-              const unsigned long long a = keys[t], b = keys[ixj];
-              const bool desc = (t & k) == 0;
-              if (desc ? (a < b) : (a > b)) { keys[t] = b; keys[ixj] = a; }
+        stop = true;
+      } else {
+        int np2 = 32;
+        while (np2 < M) np2 <<= 1;
+        for (int t = lane; t < np2; t += 32) {
+          unsigned long long key = 0ull;
+          if (t < M && cval[t] > 0.f)
+            key = (static_cast<unsigned long long>(__float_as_uint(cval[t])) << 32) | (0xFFFFFFFFull - cidx[t]);
+          keys[t] = key;
+        }
+        __syncwarp();
+        for (int k = 2; k <= np2; k <<= 1) {
+          for (int j = k >> 1; j > 0; j >>= 1) {
+            for (int t = lane; t < np2; t += 32) {
+              const int ixj = t ^ j;
+              if (ixj > t) {
+                const unsigned long long a = keys[t], b = keys[ixj];
+                const bool desc = (t & k) == 0;
+                if (desc ? (a < b) : (a > b)) { keys[t] = b; keys[ixj] = a; }
+              }
             }
+            __syncwarp();
           }
-          __syncwarp();
+        }
+        const int seg = np2 / 32;                  // contiguous positions per lane
+        const int t0 = lane * seg;
+        double local = 0.0;
+        for (int t = t0; t < t0 + seg; ++t) local += static_cast<double>(__uint_as_float(static_cast<unsigned>(keys[t] >> 32)));
+        double incl = local;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const double up = __shfl_up_sync(0xffffffffu, incl, o);
+          if (lane >= o) incl += up;
+        }
+        double running = incl - local;             // sum of the sorted scores before position t0
+        int ut = 0;
+        for (int t = t0; t < t0 + seg && t < live; ++t) {
+          const unsigned long long key = keys[t];
+          const double v = static_cast<double>(__uint_as_float(static_cast<unsigned>(key >> 32)));
+          double c;
+          if (!lag) c = fsum + s_cur + running;                       // prefix[rank-1]
+          else if (t == 0) c = (i == 1) ? 0.0 : fsum + s_lag;         // prefix[rank-2], rank = i
+          else c = fsum + s_cur + (running - static_cast<double>(__uint_as_float(static_cast<unsigned>(keys[t - 1] >> 32))));
+          if (c < req) {
+            const unsigned col = 0xFFFFFFFFu - static_cast<unsigned>(key & 0xFFFFFFFFull);
+            atomicOr(&taken[col >> 5], 1u << (col & 31));
+          } else {
+            ut = 1;
+          }
+          running += v;
+        }
+        if (__any_sync(0xffffffffu, ut)) { untaken = true; stop = true; }
+        // the prefix after all positive scores, and the one before the last of them
+        const double sorted_total = __shfl_sync(0xffffffffu, incl, 31);
+        const double last_v = static_cast<double>(__uint_as_float(static_cast<unsigned>(keys[live - 1] >> 32)));
+        s_lag = s_cur + (sorted_total - last_v);
+        s_cur += sorted_total;
+        i += live;
+        live = 0;
+        __syncwarp();
+        if (lane == 0) {
+          __threadfence_block();
+          atomicExch(&sort_lock, 0);
         }
       }
-      const int n_rem = n_others - (i - 1);
-      const int seg = p.np2 / 32;                  // contiguous positions per lane
-      const int t0 = lane * seg;
-      double local = 0.0;
-      for (int t = t0; t < t0 + seg; ++t) local += static_cast<double>(__uint_as_float(static_cast<unsigned>(keys[t] >> 32)));
-      double incl = local;
+    }
+    // ---- ranks that hold a zero score (column order).  The prefix no longer moves, so after the first of
+    // them the decision value is fsum + s_cur for all: either every remaining rank is taken, or (only when a
+    // single block is forced, whose decision values lag one rank behind) just the first one.
+    if (!stop && i <= n_others) {
+      const double c = lag ? (i == 1 ? 0.0 : fsum + s_lag) : fsum + s_cur;
+      if (!(c < req)) {
+        untaken = true;
+      } else if (fsum + s_cur < req) {
+        for (int t = lane; t < W; t += 32) taken[t] |= ~cand[t] & valid(t);
+      } else {
+        // lowest zero-score column that is not forced
+        int best = 0x7fffffff;
+        for (int t = lane; t < W; t += 32) {
+          const uint32_t z = ~(cand[t] | taken[t]) & valid(t);
+          if (z && best == 0x7fffffff) best = 32 * t + __ffs(z) - 1;
+        }
 #pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const double up = __shfl_up_sync(0xffffffffu, incl, o);
-        if (lane >= o) incl += up;
-      }
-      double running = incl - local;               // sum of the sorted scores before position t0
-      int ut = 0;
-      for (int t = t0; t < t0 + seg && t < n_rem; ++t) {
-        const unsigned long long key = keys[t];
-        const double v = static_cast<double>(__uint_as_float(static_cast<unsigned>(key >> 32)));
-        double c;
-        if (!lag) c = fsum + s_cur + running;                       // prefix[rank-1]
-        else if (t == 0) c = fsum + s_lag;                          // prefix[rank-2], rank = i
-        else c = fsum + s_cur + (running - static_cast<double>(__uint_as_float(static_cast<unsigned>(keys[t - 1] >> 32))));
-        if (c < req) mrow[0xFFFFFFFFu - static_cast<unsigned>(key & 0xFFFFFFFFull)] = 1;
-        else ut = 1;
-        running += v;
-      }
-      if (__any_sync(0xffffffffu, ut)) untaken = true;
-      __syncwarp();
-      if (lane == 0) {
-        __threadfence_block();
-        atomicExch(&sort_lock, 0);
+        for (int o = 16; o > 0; o >>= 1) {
+          const int ob = __shfl_xor_sync(0xffffffffu, best, o);
+          best = ob < best ? ob : best;
+        }
+        if (lane == 0 && best != 0x7fffffff) taken[best >> 5] |= 1u << (best & 31);
+        if (i < n_others) untaken = true;          // the next rank compares fsum + s_cur >= req
       }
     }
   }
   __syncwarp();
-  if (untaken && lane == 0) mrow[0] = 1;
+  if (untaken && lane == 0) taken[0] |= 1u;
   __syncwarp();
 
-  // post-processing + outputs
+  // ---- post-processing + outputs, one 32-column word per lane
   const bool want_list = idx_out && cnt_out && R < p.list_q_blocks;
   int32_t* lrow = want_list ? idx_out + (static_cast<size_t>(bh) * p.list_q_blocks + R) * p.list_k_blocks : nullptr;
   uint8_t* mo = mask_out ? mask_out + static_cast<size_t>(w) * N : nullptr;
+  int hi_keep = N - 1;                             // causal clean-up: columns above are cleared
+  if (p.causal) {
+    hi_keep = cur + p.bpc - 1;
+    if (p.diagonal_cleanup && p.block_offset + R < hi_keep) hi_keep = p.block_offset + R;
+  }
+  int hi_list = p.list_k_blocks - 1;               // columns the block list may hold
+  if (p.causal) {
+    // last token of query block R sees keys up to this position (query end aligned to key end)
+    int last_q = R * 128 + 127;
+    if (last_q > p.list_q_len - 1) last_q = p.list_q_len - 1;
+    const long long lim = static_cast<long long>(last_q) + (p.list_k_len - p.list_q_len);
+    const int jm = lim < 0 ? -1 : static_cast<int>(lim / 128);
+    if (jm < hi_list) hi_list = jm;
+  }
+  const int recent = p.block_offset + R;
   int base = 0;
-  for (int j0 = 0; j0 < N; j0 += 32) {
-    const int j = j0 + lane;
-    int m = 0;
-    if (j < N) {
-      m = mrow[j];
-      if (p.causal && (j >= cur + p.bpc || (p.diagonal_cleanup && j > p.block_offset + R))) m = 0;
-      if (p.keep_sink && R == 0) m = 1;
-      if (p.keep_recent && j == p.block_offset + R) m = 1;
-      if (mo) mo[j] = static_cast<uint8_t>(m);
+  for (int t0 = 0; t0 < W; t0 += 32) {
+    const int t = t0 + lane;
+    uint32_t word = 0u;
+    if (t < W) {
+      word = taken[t] & valid(t) & bits_le(hi_keep, t);
+      if (p.keep_sink && R == 0) word = valid(t);
+      if (p.keep_recent && recent < N && (recent >> 5) == t) word |= 1u << (recent & 31);
+      if (mo) {
+        if (p.vec4 && 32 * t + 32 <= N) {
+          uint32_t b[8];
+#pragma unroll
+          for (int q = 0; q < 8; ++q) b[q] = (((word >> (4 * q)) & 15u) * 0x00204081u) & 0x01010101u;
+          uint4* dst = reinterpret_cast<uint4*>(mo + 32 * t);
+          dst[0] = make_uint4(b[0], b[1], b[2], b[3]);
+          dst[1] = make_uint4(b[4], b[5], b[6], b[7]);
+        } else {
+          for (int q = 0; q < 32 && 32 * t + q < N; ++q) mo[32 * t + q] = static_cast<uint8_t>((word >> q) & 1u);
+        }
+      }
     }
     if (want_list) {
-      const int keep = (m && j < p.list_k_blocks && list_keeps(p.causal, R, j, p.list_q_len, p.list_k_len)) ? 1 : 0;
-      const unsigned bal = __ballot_sync(0xffffffffu, keep);
-      if (keep) lrow[base + __popc(bal & ((1u << lane) - 1u))] = j;
-      base += __popc(bal);
+      uint32_t lw = t < W ? word & bits_le(hi_list, t) : 0u;
+      const int c = __popc(lw);
+      int incl = c;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+      }
+      int pos = base + incl - c;
+      while (lw) {
+        lrow[pos++] = 32 * t + __ffs(lw) - 1;
+        lw &= lw - 1;
+      }
+      base += __shfl_sync(0xffffffffu, incl, 31);
     }
   }
   if (want_list && lane == 0) cnt_out[static_cast<size_t>(bh) * p.list_q_blocks + R] = base;
+}
+
+__device__ __forceinline__ bool list_keeps(int causal, int R, int j, int list_q_len, int list_k_len) {
+  if (!causal) return true;
+  // last token of query block R sees keys up to this position (query end aligned to key end)
+  int last_q = R * 128 + 127;
+  if (last_q > list_q_len - 1) last_q = list_q_len - 1;
+  return static_cast<long long>(j) * 128 <= static_cast<long long>(last_q) + (list_k_len - list_q_len);
 }
 
 // One warp per (head, query-block) row of a caller-supplied mask.
@@ -276,9 +427,14 @@ int select_launch(const float* attn_sums, int batch, int heads, int q_blocks, in
   int np2 = 32;
   while (np2 < k_blocks) np2 <<= 1;
   p.np2 = np2;
+  p.words = (k_blocks + 31) / 32;
   p.vals_bytes = (k_blocks * 4 + 15) & ~15;
+  p.idx_bytes = (k_blocks * 2 + 15) & ~15;
   p.keys_bytes = np2 * 8;
-  p.per_warp_bytes = p.vals_bytes + ((k_blocks + 15) & ~15);
+  p.per_warp_bytes = p.vals_bytes + p.idx_bytes + ((2 * p.words * 4 + 15) & ~15);
+  // 16-byte accesses to the rows of the scores and of the mask
+  p.vec4 = (k_blocks % 16 == 0 && (reinterpret_cast<uintptr_t>(attn_sums) & 15) == 0 &&
+            (mask == nullptr || (reinterpret_cast<uintptr_t>(mask) & 15) == 0)) ? 1 : 0;
   int wpc = (48 * 1024 - p.keys_bytes) / p.per_warp_bytes;
   wpc = wpc < 1 ? 1 : (wpc > 8 ? 8 : wpc);
   p.warps_per_cta = wpc;
