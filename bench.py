@@ -266,10 +266,12 @@ def run_gpu_arm(args):
     n_sel = 0
     for it in range(reps + 1):
         ev[0].record()
-        sums = ops.estimate_block_sums(dq, dk, w.stride, 128, chunk, 1.0, w.causal)
+        band = ops.band_applies(w.seq_len, chunk, w.causal)          # what Xattention_prefill does
+        sums = ops.estimate_block_sums(dq, dk, w.stride, 128, chunk, 1.0, w.causal, band=band)
         ev[1].record()
         mask, idx, cnt = ops.select_blocks(sums, g["bpc"], g["block_offset"], w.threshold, w.causal, True,
-                                           list_shape=(w.seq_len, w.seq_len))
+                                           list_shape=(w.seq_len, w.seq_len), want_mask=False,
+                                           band_k_blocks=g["kb"] if band else None)
         ev[2].record()
         ops.block_sparse_attention(dq, dk, dv, idx, cnt, w.causal)
         ev[3].record()

@@ -37,6 +37,11 @@ extern "C" {
 /* estimate semantics: which of the reference's two code paths to reproduce */
 #define XATTN_B200_SEMANTICS_TORCH 0  /* torch branch, xattn/src/Xattention.py:174-252 (what the reference runs on a B200) */
 #define XATTN_B200_SEMANTICS_TRITON 1 /* Triton kernels, xattn/src/kernels.py:5-156,197-235 */
+/* The torch branch with attn_sums in CHUNK-BAND layout [batch, hq, q_blocks_pad, chunk_size/block_size]: when the
+ * keys are not padded the torch branch leaves every column outside the row's own chunk at zero, so only the
+ * chunk's own key blocks (columns current_index .. current_index + blocks_per_chunk) are written.  Causal and
+ * k_len % chunk_size == 0 only (XATTN_B200_ERR_ARG otherwise).  Feed the result to xattn_b200_select_band. */
+#define XATTN_B200_SEMANTICS_TORCH_BAND 2
 
 /* status codes */
 #define XATTN_B200_OK 0
@@ -167,6 +172,18 @@ int xattn_b200_select(const float* attn_sums, int batch, int heads, int q_blocks
                       const float* threshold_per_head, int keep_sink, int keep_recent, uint8_t* mask,
                       int32_t* block_idx, int32_t* block_cnt, int list_q_blocks, int list_k_blocks, int list_q_len,
                       int list_k_len, int* status, void* cuda_stream);
+
+/*
+ * xattn_b200_select for attn_sums in chunk-band layout (XATTN_B200_SEMANTICS_TORCH_BAND): attn_sums is
+ * [batch, heads, q_blocks, blocks_per_chunk]; entry c of row R is the score of key block current_index + c, every
+ * other key block has score zero.  Same rule, same outputs (mask and lists are over all k_blocks columns), but a
+ * row is blocks_per_chunk values instead of k_blocks.  Causal only.
+ */
+int xattn_b200_select_band(const float* attn_sums, int batch, int heads, int q_blocks, int k_blocks,
+                           int blocks_per_chunk, int block_offset, int causal, int diagonal_cleanup, double threshold,
+                           const float* threshold_per_head, int keep_sink, int keep_recent, uint8_t* mask,
+                           int32_t* block_idx, int32_t* block_cnt, int list_q_blocks, int list_k_blocks,
+                           int list_q_len, int list_k_len, int* status, void* cuda_stream);
 
 /*
  * Block mask -> per-row block lists, for callers that bring their own mask (the `base_blockmask`

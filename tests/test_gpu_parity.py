@@ -578,6 +578,34 @@ def test_llama_rope_and_attend_equals_the_composed_reference_steps():
     assert torch.equal(kp.view(B, L, Hkv, D).transpose(1, 2).cpu(), k_ref)     # rotated keys left for the cache
 
 
+@pytest.mark.parametrize("name,L,Lq,chunk", [("llama3_8b_32k", 8192, 8192, 2048), ("llama3_8b_128k", 8192, 8192, 2048),
+                                             ("llama3_8b_32k", 8192, 4096, 4096), ("llama3_8b_32k", 6144, 6144, 2048)])
+def test_chunk_band_layout_equals_the_dense_one(name, L, Lq, chunk):
+    """Un-padded causal keys under the torch branch: the sums kept as a chunk-wide band, and the selection run
+    on the band, give exactly the dense layout's sums, mask and block lists."""
+    from xattn_b200 import ops, synth
+    q, k, v, w = synth.make_inputs(name, seed=11, heads_limit=1, seq_len=L)
+    q, k = q[:, :, L - Lq:].to(DEV), k.to(DEV)
+    assert ops.band_applies(L, chunk, True)
+    g = ops.geometry(Lq, L, chunk, w.stride)
+    dense = ops.estimate_block_sums(q, k, w.stride, 128, chunk, 1.0, True)
+    band = ops.estimate_block_sums(q, k, w.stride, 128, chunk, 1.0, True, band=True)
+    assert band.shape == (1, q.shape[1], g["qb"], g["bpc"])
+    rebuilt = torch.zeros_like(dense)
+    for c in range(g["qb"] // g["bpc"]):
+        cur = g["block_offset"] + c * g["bpc"]
+        rows = slice(c * g["bpc"], (c + 1) * g["bpc"])
+        rebuilt[:, :, rows, cur:cur + g["bpc"]] = band[:, :, rows]
+    assert torch.equal(rebuilt, dense)
+    for thr in (0.9, torch.linspace(0.5, 1.0, q.shape[1])):
+        m0, i0, c0 = ops.select_blocks(dense, g["bpc"], g["block_offset"], thr, True, True, list_shape=(Lq, L))
+        m1, i1, c1 = ops.select_blocks(band, g["bpc"], g["block_offset"], thr, True, True, list_shape=(Lq, L),
+                                       band_k_blocks=g["kb"])
+        assert torch.equal(m0, m1) and torch.equal(c0, c1)
+        valid = torch.arange(i0.shape[-1], device=DEV)[None, None, None, :] < c0[..., None]
+        assert torch.equal(i0[valid], i1[valid])
+
+
 def test_runs_are_bit_identical():
     """Same inputs, two runs: identical bits (no race between the roles of a CTA)."""
     import xattn_b200

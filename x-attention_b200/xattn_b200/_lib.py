@@ -11,7 +11,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libxattn_b200.so")
 
 BF16, F16 = 0, 1
-SEMANTICS_TORCH, SEMANTICS_TRITON = 0, 1
+SEMANTICS_TORCH, SEMANTICS_TRITON, SEMANTICS_TORCH_BAND = 0, 1, 2
 
 _i, _i64, _f, _d, _p, _sz = C.c_int, C.c_int64, C.c_float, C.c_double, C.c_void_p, C.c_size_t
 
@@ -30,6 +30,8 @@ SIGNATURES = {
     "xattn_b200_rope_qk": (_i, [_p, _p, _i, _i, _i, _i, _i, _i, _i64, _i64, _i64, _i64, _i64, _i64, _p, _p, _i64, _i64, _p]),
     "xattn_b200_select": (_i, [_p, _i, _i, _i, _i, _i, _i, _i, _i, _d, _p, _i, _i, _p, _p, _p,
                                _i, _i, _i, _i, _p, _p]),
+    "xattn_b200_select_band": (_i, [_p, _i, _i, _i, _i, _i, _i, _i, _i, _d, _p, _i, _i, _p, _p, _p,
+                                    _i, _i, _i, _i, _p, _p]),
     "xattn_b200_mask_to_lists": (_i, [_p, _i, _i, _i, _i, _i, _i, _i, _p, _p, _p]),
     "xattn_b200_block_sparse_attn": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _i, _i,
                                           _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64,

@@ -124,8 +124,11 @@ def Xattention_prefill(
     if value_states.device != dev:
         value_states = value_states.to(dev)
     g = ops.geometry(Lq, Lk, chunk_size, stride, block_size)
+    # un-padded causal keys under the torch branch: the sums outside a row's own chunk are zero and are not kept
+    band = ops.band_applies(Lk, chunk_size, bool(causal))
     sums = ops.estimate_block_sums(query_states, key_states, stride, block_size, chunk_size, float(norm),
-                                   bool(causal))
+                                   bool(causal), band=band)
     _, idx, cnt = ops.select_blocks(sums, g["bpc"], g["block_offset"], threshold, bool(causal), True,
-                                    bool(keep_sink), bool(keep_recent), list_shape=(Lq, Lk), want_mask=False)
+                                    bool(keep_sink), bool(keep_recent), list_shape=(Lq, Lk), want_mask=False,
+                                    band_k_blocks=g["kb"] if band else None)
     return ops.block_sparse_attention(query_states, key_states, value_states, idx, cnt, bool(causal))

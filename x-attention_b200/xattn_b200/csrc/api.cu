@@ -15,7 +15,7 @@ int rope_qk_launch(void* q, void* k, int dtype, int batch, int hq, int hkv, int 
 int select_launch(const float* attn_sums, int batch, int heads, int q_blocks, int k_blocks, int bpc, int block_offset,
                   int causal, int diagonal_cleanup, double threshold, const float* thr_per_head, int keep_sink,
                   int keep_recent, uint8_t* mask, int32_t* block_idx, int32_t* block_cnt, int list_q_blocks,
-                  int list_k_blocks, int list_q_len, int list_k_len, int* status, cudaStream_t stream);
+                  int list_k_blocks, int list_q_len, int list_k_len, int band, int* status, cudaStream_t stream);
 int mask_to_lists_launch(const uint8_t* mask, int batch, int heads, int mask_q_blocks, int mask_k_blocks, int q_len,
                          int k_len, int causal, int32_t* block_idx, int32_t* block_cnt, cudaStream_t stream);
 int block_sparse_attn_launch(const void* q, const void* k, const void* v, int dtype, int batch, int hq, int hkv,
@@ -102,7 +102,18 @@ int xattn_b200_select(const float* attn_sums, int batch, int heads, int q_blocks
                       int list_k_len, int* status, void* cuda_stream) {
   return xb::select_launch(attn_sums, batch, heads, q_blocks, k_blocks, blocks_per_chunk, block_offset, causal,
                            diagonal_cleanup, threshold, threshold_per_head, keep_sink, keep_recent, mask, block_idx,
-                           block_cnt, list_q_blocks, list_k_blocks, list_q_len, list_k_len, status,
+                           block_cnt, list_q_blocks, list_k_blocks, list_q_len, list_k_len, 0, status,
+                           static_cast<cudaStream_t>(cuda_stream));
+}
+
+int xattn_b200_select_band(const float* attn_sums, int batch, int heads, int q_blocks, int k_blocks,
+                           int blocks_per_chunk, int block_offset, int causal, int diagonal_cleanup, double threshold,
+                           const float* threshold_per_head, int keep_sink, int keep_recent, uint8_t* mask,
+                           int32_t* block_idx, int32_t* block_cnt, int list_q_blocks, int list_k_blocks,
+                           int list_q_len, int list_k_len, int* status, void* cuda_stream) {
+  return xb::select_launch(attn_sums, batch, heads, q_blocks, k_blocks, blocks_per_chunk, block_offset, causal,
+                           diagonal_cleanup, threshold, threshold_per_head, keep_sink, keep_recent, mask, block_idx,
+                           block_cnt, list_q_blocks, list_k_blocks, list_q_len, list_k_len, 1, status,
                            static_cast<cudaStream_t>(cuda_stream));
 }
 

@@ -45,6 +45,8 @@ struct EstGeom {
   int rbs, kb_total, qb_total;
   int n_mtiles, n_ntiles;
   int tile_n;                  // columns per tile: 256, or 128 when no row sees more than 128 columns
+  int band;                    // attn_sums holds only the chunk's own key blocks (left_blank only): row stride bpc
+  int bpc;                     // key blocks per chunk
   float scale_log2;
 };
 
@@ -562,10 +564,13 @@ __global__ void __launch_bounds__(256)
 est_blocksum_kernel(const EstGeom g, const int* __restrict__ tile_lo, const int* __restrict__ tile_prefix,
                     const float* __restrict__ partial, const float2* __restrict__ mtile,
                     const float2* __restrict__ rowstat, float* __restrict__ sums) {
-  const int kb = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
   const int qb = blockIdx.y, bh = blockIdx.z;
-  if (kb >= g.kb_total) return;
   const int i0 = qb * g.rbs;
+  // band layout: only the key blocks of the query block's own chunk, [cur, cur + bpc)
+  const int cur = g.band ? (g.row_off + (i0 / g.rcs) * g.rcs) / g.rbs : 0;
+  const int kb_local = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
+  if (kb_local >= (g.band ? g.bpc : g.kb_total)) return;
+  const int kb = cur + kb_local;
   const int mt = i0 / kTileM;
   const int nlo = __ldg(tile_lo + mt);
   const int ncnt = __ldg(tile_prefix + mt + 1) - __ldg(tile_prefix + mt);
@@ -592,7 +597,7 @@ est_blocksum_kernel(const EstGeom g, const int* __restrict__ tile_lo, const int*
       }
     }
   }
-  float* out = sums + (static_cast<size_t>(bh) * g.qb_total + qb) * g.kb_total + kb;
+  float* out = sums + (static_cast<size_t>(bh) * g.qb_total + qb) * (g.band ? g.bpc : g.kb_total) + kb_local;
   if (VEC == 4) *reinterpret_cast<float4*>(out) = make_float4(acc[0], acc[1 % VEC], acc[2 % VEC], acc[3 % VEC]);
   else out[0] = acc[0];
 }
@@ -646,7 +651,10 @@ static int fill_geometry(int batch, int hq, int hkv, int q_len, int k_len, int h
   g.rcs = chunk_size / stride;
   g.row_off = (lk / chunk_size - lq / chunk_size) * g.rcs;
   g.causal = causal ? 1 : 0;
-  g.left_blank = (causal && semantics == XATTN_B200_SEMANTICS_TORCH && k_pad / stride == 0) ? 1 : 0;
+  g.left_blank = (causal && semantics != XATTN_B200_SEMANTICS_TRITON && k_pad / stride == 0) ? 1 : 0;
+  g.band = semantics == XATTN_B200_SEMANTICS_TORCH_BAND ? 1 : 0;
+  g.bpc = chunk_size / block_size;
+  if (g.band && !g.left_blank) return XATTN_B200_ERR_ARG;
   g.rbs = block_size / stride;
   g.kb_total = lk / block_size; g.qb_total = lq / block_size;
   g.n_mtiles = (g.rows_total + kTileM - 1) / kTileM;
@@ -687,7 +695,9 @@ int estimate_launch(const void* q, const void* k, int dtype, int batch, int hq, 
                     float* attn_sums, void* workspace, size_t workspace_bytes, int* status, cudaStream_t stream) {
   if (!q || !k || !attn_sums) return XATTN_B200_ERR_ARG;
   if (dtype != XATTN_B200_BF16 && dtype != XATTN_B200_F16) return XATTN_B200_ERR_ARG;
-  if (semantics != XATTN_B200_SEMANTICS_TORCH && semantics != XATTN_B200_SEMANTICS_TRITON) return XATTN_B200_ERR_ARG;
+  if (semantics != XATTN_B200_SEMANTICS_TORCH && semantics != XATTN_B200_SEMANTICS_TRITON &&
+      semantics != XATTN_B200_SEMANTICS_TORCH_BAND)
+    return XATTN_B200_ERR_ARG;
   if (!(scale > 0.f)) return XATTN_B200_ERR_ARG;
   EstGeom g;
   int rc = fill_geometry(batch, hq, hkv, q_len, k_len, head_dim, stride, block_size, chunk_size, scale, causal,
@@ -801,8 +811,9 @@ int estimate_launch(const void* q, const void* k, int dtype, int batch, int hq, 
   est_rowstat_kernel<<<static_cast<int>((total_rows + 255) / 256), 256, 0, stream>>>(
       g, tile_lo, tile_prefix, mtile, rowstat, static_cast<int>(total_rows));
   if ((rc = launch_status())) return rc;
-  const bool vec4 = g.kb_total % 4 == 0 && (reinterpret_cast<uintptr_t>(attn_sums) & 15) == 0;
-  const int per_row = vec4 ? g.kb_total / 4 : g.kb_total;
+  const int out_cols = g.band ? g.bpc : g.kb_total;
+  const bool vec4 = g.kb_total % 4 == 0 && out_cols % 4 == 0 && (reinterpret_cast<uintptr_t>(attn_sums) & 15) == 0;
+  const int per_row = vec4 ? out_cols / 4 : out_cols;
   const int bt = per_row >= 256 ? 256 : ((per_row + 31) / 32) * 32;
   const dim3 fgrid((per_row + bt - 1) / bt, g.qb_total, batch * hq);
   if (vec4)

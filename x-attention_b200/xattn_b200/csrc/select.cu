@@ -37,7 +37,9 @@ struct SelParams {
   int words;          // 32-column words per row
   int vals_bytes, idx_bytes, keys_bytes, per_warp_bytes;   // keys: one sort buffer per CTA, taken in turn by its warps
   int rows_total;
-  int vec4;           // rows can be read as float4 / masks written as 16-byte vectors
+  int vec_in;         // score rows can be read as float4
+  int vec_mask;       // mask rows can be written as 16-byte vectors
+  int band;           // score rows hold only the chunk's own key blocks [cur, cur + bpc)
 };
 
 __device__ __forceinline__ double warp_sum(double v) {
@@ -79,7 +81,6 @@ __global__ void select_kernel(const float* __restrict__ sums, const SelParams p,
   const int h = bh % p.heads;
   const int N = p.k_blocks;
   const int W = p.words;
-  const float* x = sums + static_cast<size_t>(w) * N;
   auto valid = [&](int t) -> uint32_t { return bits_le(N - 1, t); };
 
   const int cur = p.block_offset + (R / p.bpc) * p.bpc;
@@ -88,6 +89,10 @@ __global__ void select_kernel(const float* __restrict__ sums, const SelParams p,
   const int n_forced = p.causal ? (f0 ? 2 : 1) : 0;
   const int lag = n_forced == 1 ? 1 : 0;
   const int n_others = N - n_forced;
+  // stored part of the row: `n_read` scores, the first of them belongs to column `col0`; the rest are zero
+  const int n_read = p.band ? p.bpc : N;
+  const int col0 = p.band ? cur : 0;
+  const float* x = sums + static_cast<size_t>(w) * n_read;
 
   for (int t = lane; t < W; t += 32) { taken[t] = 0u; cand[t] = 0u; }
   __syncwarp();
@@ -97,48 +102,43 @@ __global__ void select_kernel(const float* __restrict__ sums, const SelParams p,
   int M = 0;                                       // positive non-forced scores so far (warp-uniform)
   // 1024 columns at a time: all loads of the piece are issued before any of it is processed, so a row costs one
   // memory round trip per 1024 columns instead of one per 128
-  for (int j1 = 0; j1 < N; j1 += 1024) {
+  for (int j1 = 0; j1 < n_read; j1 += 1024) {
     float vv[8][4];
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
       const int j = j1 + u * 128 + 4 * lane;
 #pragma unroll
       for (int e = 0; e < 4; ++e) vv[u][e] = 0.f;
-      if (p.vec4) {
-        if (j < N) {
+      if (p.vec_in) {
+        if (j < n_read) {
           const float4 q = __ldg(reinterpret_cast<const float4*>(x + j));
           vv[u][0] = q.x; vv[u][1] = q.y; vv[u][2] = q.z; vv[u][3] = q.w;
         }
       } else {
 #pragma unroll
         for (int e = 0; e < 4; ++e)
-          if (j + e < N) vv[u][e] = __ldg(x + j + e);
+          if (j + e < n_read) vv[u][e] = __ldg(x + j + e);
       }
     }
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
       const int j0 = j1 + u * 128;
-      if (j0 >= N) break;
+      if (j0 >= n_read) break;
       const int j = j0 + 4 * lane;
       const float (&v)[4] = vv[u];
       uint32_t nib = 0u;
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const int jj = j + e;
-        if (jj < N) {
+        const int jj = col0 + j + e;              // column
+        if (j + e < n_read) {
           part += static_cast<double>(v[e]);
           const bool forced = p.causal && (jj == d || (f0 && jj == 0));
           if (forced) fpart += static_cast<double>(v[e]);
           else if (v[e] > 0.f) nib |= 1u << e;
         }
       }
-      // candidate bitmap: eight lanes share a word
-      uint32_t word = nib << (4 * (lane & 7));
-      word |= __shfl_xor_sync(0xffffffffu, word, 1);
-      word |= __shfl_xor_sync(0xffffffffu, word, 2);
-      word |= __shfl_xor_sync(0xffffffffu, word, 4);
-      const int wi = (j0 >> 5) + (lane >> 3);
-      if ((lane & 7) == 0 && wi < W) cand[wi] = word;
+      // candidate bitmap (col0 and j are multiples of 4, so the four bits stay inside one word)
+      if (nib) atomicOr(&cand[(col0 + j) >> 5], nib << ((col0 + j) & 31));
       // compaction in column order (rows are sparse: skip the scan when the piece holds no positive score)
       if (__any_sync(0xffffffffu, nib != 0u)) {
         const int c = __popc(nib);
@@ -153,7 +153,7 @@ __global__ void select_kernel(const float* __restrict__ sums, const SelParams p,
         for (int e = 0; e < 4; ++e)
           if ((nib >> e) & 1u) {
             cval[pos] = v[e];
-            cidx[pos] = static_cast<uint16_t>(j + e);
+            cidx[pos] = static_cast<uint16_t>(col0 + j + e);
             ++pos;
           }
         M += __shfl_sync(0xffffffffu, incl, 31);
@@ -343,7 +343,7 @@ __global__ void select_kernel(const float* __restrict__ sums, const SelParams p,
       if (p.keep_sink && R == 0) word = valid(t);
       if (p.keep_recent && recent < N && (recent >> 5) == t) word |= 1u << (recent & 31);
       if (mo) {
-        if (p.vec4 && 32 * t + 32 <= N) {
+        if (p.vec_mask && 32 * t + 32 <= N) {
           uint32_t b[8];
 #pragma unroll
           for (int q = 0; q < 8; ++q) b[q] = (((word >> (4 * q)) & 15u) * 0x00204081u) & 0x01010101u;
@@ -407,10 +407,13 @@ __global__ void mask_to_lists_kernel(const uint8_t* __restrict__ mask, int rows_
 int select_launch(const float* attn_sums, int batch, int heads, int q_blocks, int k_blocks, int bpc, int block_offset,
                   int causal, int diagonal_cleanup, double threshold, const float* thr_per_head, int keep_sink, int keep_recent,
                   uint8_t* mask, int32_t* block_idx, int32_t* block_cnt, int list_q_blocks, int list_k_blocks,
-                  int list_q_len, int list_k_len, int* status, cudaStream_t stream) {
+                  int list_q_len, int list_k_len, int band, int* status, cudaStream_t stream) {
   if (!attn_sums || batch < 1 || heads < 1 || q_blocks < 1 || k_blocks < 1 || bpc < 1 || block_offset < 0)
     return XATTN_B200_ERR_ARG;
   if (k_blocks > 8192) return XATTN_B200_ERR_LIMIT;
+  // band layout: the stored columns are the chunk's own ones, which needs the causal chunk structure and a
+  // column origin that keeps groups of four inside a 32-column word
+  if (band && (!causal || bpc % 4 != 0 || block_offset % 4 != 0)) return XATTN_B200_ERR_ARG;
   if (q_blocks % bpc != 0) return XATTN_B200_ERR_ARG;
   if (causal && block_offset + q_blocks > k_blocks) return XATTN_B200_ERR_ARG;
   if ((block_idx == nullptr) != (block_cnt == nullptr)) return XATTN_B200_ERR_ARG;
@@ -432,9 +435,11 @@ int select_launch(const float* attn_sums, int batch, int heads, int q_blocks, in
   p.idx_bytes = (k_blocks * 2 + 15) & ~15;
   p.keys_bytes = np2 * 8;
   p.per_warp_bytes = p.vals_bytes + p.idx_bytes + ((2 * p.words * 4 + 15) & ~15);
+  p.band = band ? 1 : 0;
   // 16-byte accesses to the rows of the scores and of the mask
-  p.vec4 = (k_blocks % 16 == 0 && (reinterpret_cast<uintptr_t>(attn_sums) & 15) == 0 &&
-            (mask == nullptr || (reinterpret_cast<uintptr_t>(mask) & 15) == 0)) ? 1 : 0;
+  const int n_read = band ? bpc : k_blocks;
+  p.vec_in = (n_read % 4 == 0 && (reinterpret_cast<uintptr_t>(attn_sums) & 15) == 0) ? 1 : 0;
+  p.vec_mask = (k_blocks % 16 == 0 && mask != nullptr && (reinterpret_cast<uintptr_t>(mask) & 15) == 0) ? 1 : 0;
   int wpc = (48 * 1024 - p.keys_bytes) / p.per_warp_bytes;
   wpc = wpc < 1 ? 1 : (wpc > 8 ? 8 : wpc);
   p.warps_per_cta = wpc;

@@ -100,6 +100,7 @@ def Xattention_prefill_host(query_states: torch.Tensor, key_states: torch.Tensor
     if out is None:
         out = torch.empty(1, Hq, Lq, D, dtype=cdtype).pin_memory()
     g = ops.geometry(Lq, Lk, chunk_size, stride, block_size)
+    band = ops.band_applies(Lk, chunk_size, bool(causal))
     slices = group_slices(Hq, Hkv, groups_per_step)
     nk = slices[0][3] - slices[0][2]
     # smaller steps shorten what cannot overlap: the first step's input copy and the last step's output copy
@@ -143,9 +144,11 @@ def Xattention_prefill_host(query_states: torch.Tensor, key_states: torch.Tensor
             compute.wait_event(c["loaded_k"])
             thr = threshold[q0:q1] if isinstance(threshold, torch.Tensor) else threshold
             qd, kd, vd = b["q"][:, :hq_n], c["k"][:, :hk_n], c["v"][:, :hk_n]
-            sums = ops.estimate_block_sums(qd, kd, stride, block_size, chunk_size, float(norm), bool(causal))
+            sums = ops.estimate_block_sums(qd, kd, stride, block_size, chunk_size, float(norm), bool(causal),
+                                           band=band)
             _, idx, cnt = ops.select_blocks(sums, g["bpc"], g["block_offset"], thr, bool(causal), True,
-                                            bool(keep_sink), bool(keep_recent), list_shape=(Lq, Lk), want_mask=False)
+                                            bool(keep_sink), bool(keep_recent), list_shape=(Lq, Lk), want_mask=False,
+                                            band_k_blocks=g["kb"] if band else None)
             compute.wait_event(c["loaded_v"])
             if b["used"]:
                 compute.wait_event(b["stored"])            # output buffer of step i-2 has left the device

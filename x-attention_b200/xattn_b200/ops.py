@@ -106,10 +106,21 @@ def _aligned16(x: torch.Tensor) -> torch.Tensor:
 
 
 # ------------------------------------------------------------------------------ phase 1
+def band_applies(k_len: int, chunk_size: int, causal: bool, semantics: Optional[str] = None) -> bool:
+    """True when the estimate leaves every key block outside a row's own chunk at zero (the reference's torch
+    branch on un-padded keys, xattn/src/Xattention.py:201), so that the sums can be kept as a chunk-wide band.
+    (Block counts that are not multiples of four keep the dense layout.)"""
+    return (bool(causal) and (semantics or _estimate_semantics) == "torch" and k_len % chunk_size == 0
+            and (chunk_size // 128) % 4 == 0)
+
+
 def estimate_block_sums(q: torch.Tensor, k: torch.Tensor, stride: int, block_size: int = 128,
                         chunk_size: int = 16384, norm: float = 1.0, causal: bool = True,
-                        semantics: Optional[str] = None) -> torch.Tensor:
+                        semantics: Optional[str] = None, band: bool = False) -> torch.Tensor:
     """fp32 attn_sums [B, Hq, q_blocks_pad, k_blocks_pad] of the antidiagonal estimate.
+
+    band=True (see band_applies): only the key blocks of each row's own chunk are produced,
+    [B, Hq, q_blocks_pad, chunk_size/block_size]; every other block has sum zero under the torch branch.
 
     q [B,Hq,Lq,D], k [B,Hkv,Lk,D] in bf16/fp16, or fp32 (split into three bf16 terms on the device so
     that the tensor-core product keeps fp32 accuracy)."""
@@ -118,6 +129,10 @@ def estimate_block_sums(q: torch.Tensor, k: torch.Tensor, stride: int, block_siz
     B, Hq, Lq, D = q.shape
     Hkv, Lk = k.shape[1], k.shape[2]
     sem = _SEM[semantics or _estimate_semantics]
+    if band:
+        if not band_applies(Lk, chunk_size, causal, semantics):
+            raise ValueError("band layout needs the torch branch, causal, and k_len a multiple of chunk_size")
+        sem = _lib.SEMANTICS_TORCH_BAND
     scale = 1.0 / math.sqrt(D) / stride / norm
     q = _pad_to_stride(q, stride)
     k = _pad_to_stride(k, stride)
@@ -144,7 +159,7 @@ def estimate_block_sums(q: torch.Tensor, k: torch.Tensor, stride: int, block_siz
         raise ValueError("unsupported estimate geometry (stride must be 4/8/16/32, block_size 128, "
                          "chunk_size a multiple of 128)")
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
-    sums = torch.empty(B, Hq, g["qb"], g["kb"], dtype=torch.float32, device=q.device)
+    sums = torch.empty(B, Hq, g["qb"], g["bpc"] if band else g["kb"], dtype=torch.float32, device=q.device)
     st = _status(q.device)
     _lib.check(lib.xattn_b200_estimate(
         q.data_ptr(), k.data_ptr(), dt, B, Hq, Hkv, Lq_s, Lk_s, D_eff, *_strides3(q), *_strides3(k),
@@ -157,13 +172,19 @@ def estimate_block_sums(q: torch.Tensor, k: torch.Tensor, stride: int, block_siz
 def select_blocks(sums: torch.Tensor, blocks_per_chunk: int, block_offset: int,
                   threshold: Union[float, torch.Tensor], causal: bool = True, diagonal_cleanup: bool = True,
                   keep_sink: bool = False, keep_recent: bool = False,
-                  list_shape: Optional[Tuple[int, int]] = None, want_mask: bool = True):
+                  list_shape: Optional[Tuple[int, int]] = None, want_mask: bool = True,
+                  band_k_blocks: Optional[int] = None):
     """Threshold selection over fp32 sums [B,H,qb,kb].  Returns (mask bool or None, block_idx, block_cnt);
-    the lists are None unless list_shape=(q_len, k_len) is given."""
+    the lists are None unless list_shape=(q_len, k_len) is given.  band_k_blocks=kb: `sums` is the chunk band
+    [B,H,qb,blocks_per_chunk] of estimate_block_sums(band=True) and kb the full number of key blocks."""
     _require_cuda(sums)
     lib = _lib.load()
     sums = sums.float().contiguous()
     B, H, QB, KB = sums.shape
+    if band_k_blocks is not None:
+        if KB != blocks_per_chunk:
+            raise ValueError("band sums must have blocks_per_chunk columns")
+        KB = int(band_k_blocks)
     thr_ptr, thr_val = 0, 0.0
     thr_t = None
     if isinstance(threshold, torch.Tensor):
@@ -181,7 +202,8 @@ def select_blocks(sums: torch.Tensor, blocks_per_chunk: int, block_offset: int,
         lqb, lkb = (lq + 127) // 128, (lk + 127) // 128
         idx = torch.empty(B, H, lqb, lkb, dtype=torch.int32, device=sums.device)
         cnt = torch.empty(B, H, lqb, dtype=torch.int32, device=sums.device)
-    _lib.check(lib.xattn_b200_select(
+    fn = lib.xattn_b200_select_band if band_k_blocks is not None else lib.xattn_b200_select
+    _lib.check(fn(
         sums.data_ptr(), B, H, QB, KB, blocks_per_chunk, block_offset, int(causal), int(diagonal_cleanup),
         thr_val, thr_ptr, int(keep_sink), int(keep_recent),
         mask.data_ptr() if mask is not None else 0,
