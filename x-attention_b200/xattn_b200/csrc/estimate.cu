@@ -28,6 +28,7 @@ constexpr int kTileM = 128;
 constexpr int kTileN = 256;                                  // widest column tile; EstGeom::tile_n is 256 or 128
 constexpr int kTileK = 64;                                   // elements per TMA box row = 128 bytes
 constexpr int kStages = 4;
+constexpr int kMaxStages = 6;                                // stages of the kernels whose stage is 32 KiB
 constexpr int kABytes = kTileM * kTileK * 2;                 // 16 KiB
 constexpr int kBBytes = kTileN * kTileK * 2;                 // 32 KiB
 constexpr int kStageBytes = kABytes + kBBytes;               // 48 KiB
@@ -218,19 +219,23 @@ est_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 float2* __restrict__ mtile, const uint32_t idesc, int* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // 128-column tiles (every operand tile is used once: the kernel streams Q and K from HBM) take six 32 KiB
+  // stages, 256-column tiles four 48 KiB ones: 192 KiB in flight either way
+  const int n_stages = g.tile_n == 128 ? kMaxStages : kStages;
+  const int stage_bytes = kABytes + g.tile_n * kTileK * 2;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
-  const uint32_t full0 = smem_u32(bars);                    // [kStages]
-  const uint32_t empty0 = smem_u32(bars + kStages);         // [kStages]
-  const uint32_t tfull0 = smem_u32(bars + 2 * kStages);     // [2]
-  const uint32_t tempty0 = smem_u32(bars + 2 * kStages + 2);// [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  const uint32_t full0 = smem_u32(bars);                       // [kMaxStages]
+  const uint32_t empty0 = smem_u32(bars + kMaxStages);         // [kMaxStages]
+  const uint32_t tfull0 = smem_u32(bars + 2 * kMaxStages);     // [2]
+  const uint32_t tempty0 = smem_u32(bars + 2 * kMaxStages + 2);// [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kMaxStages + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < kMaxStages; ++s) {
       mbar_init(full0 + 8 * s, 1);
       mbar_init(empty0 + 8 * s, 1);
     }
@@ -266,13 +271,13 @@ est_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         decode_tile(g.n_mtiles, tile_lo, tile_prefix, tiles_per_head, tile, bh, mt, nt);
         const int b = bh / g.hq, h = bh - b * g.hq;
         for (int ks = 0; ks < k_steps; ++ks, ++it) {
-          const int s = it % kStages;
-          const uint32_t ph = (it / kStages) & 1;
+          const int s = it % n_stages;
+          const uint32_t ph = (it / n_stages) & 1;
           if (!mbar_wait(empty0 + 8 * s, ph ^ 1, abort_flag)) break;
           const int t = ks / g.d_chunks;
           const int dc = ks - t * g.d_chunks;
-          const uint32_t dstA = smem_u32(smem + s * kStageBytes);
-          mbar_expect_tx(full0 + 8 * s, kABytes + g.tile_n * kTileK * 2);
+          const uint32_t dstA = smem_u32(smem + s * stage_bytes);
+          mbar_expect_tx(full0 + 8 * s, stage_bytes);
           tma_load_5d(dstA, &tmQ, full0 + 8 * s, dc * kTileK, g.S - 1 - t, mt * kTileM, h, b);
           tma_load_5d(dstA + kABytes, &tmK, full0 + 8 * s, dc * kTileK, t, nt * g.tile_n, h / group, b);
         }
@@ -292,13 +297,13 @@ est_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const uint32_t d_tmem = tmem_base + acc * kTileN;
         bool ok = true;
         for (int ks = 0; ks < k_steps; ++ks, ++it) {
-          const int s = it % kStages;
-          const uint32_t ph = (it / kStages) & 1;
+          const int s = it % n_stages;
+          const uint32_t ph = (it / n_stages) & 1;
           if (!mbar_wait(full0 + 8 * s, ph, abort_flag)) { ok = false; break; }
           tc_fence_after();
           // descriptors differ from the stage-0 ones only in the start-address field (units of 16 bytes)
-          const uint64_t a_desc = a_desc0 + static_cast<uint64_t>(s * (kStageBytes >> 4));
-          const uint64_t b_desc = b_desc0 + static_cast<uint64_t>(s * (kStageBytes >> 4));
+          const uint64_t a_desc = a_desc0 + static_cast<uint64_t>(s * (stage_bytes >> 4));
+          const uint64_t b_desc = b_desc0 + static_cast<uint64_t>(s * (stage_bytes >> 4));
 #pragma unroll
           for (int k4 = 0; k4 < kTileK / 16; ++k4)
             mma_ss(d_tmem, a_desc + k4 * 2, b_desc + k4 * 2, idesc, (ks > 0 || k4 > 0) ? 1u : 0u);
