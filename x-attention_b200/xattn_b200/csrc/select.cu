@@ -8,8 +8,8 @@
 // Attention rows are peaked, so the kept set is small: the warp extracts the largest remaining score
 // (lowest index on ties) one at a time, accumulating the prefix in fp64 exactly as the rule is
 // stated, and stops at the first rank that is not taken.  Rows that are still going after
-// kPeelMax extractions (flat score rows) switch to a warp-level bitonic sort of what is left plus
-// an fp64 prefix scan.  Both routes apply the same rule, so the result does not depend on the route.
+// kPeelMax extractions (flat score rows) switch to a warp-level bitonic sort of what is left (every warp
+// has its own sort buffer) plus an fp64 prefix scan.  Both routes apply the same rule, so the result does not depend on the route.
 //
 // Rule per row R (chunk c = R / bpc, current_index cur = block_offset + c*bpc, diagonal d = cur + R%bpc),
 // scores x[0..N) taken as fp64, req = sum(x) * threshold:
@@ -62,18 +62,15 @@ __global__ void select_kernel(const float* __restrict__ sums, const SelParams p,
                               const float* __restrict__ thr_per_head, uint8_t* __restrict__ mask_out,
                               int32_t* __restrict__ idx_out, int32_t* __restrict__ cnt_out, int* status) {
   extern __shared__ __align__(16) uint8_t sel_smem[];
-  __shared__ int sort_lock;
-  if (threadIdx.x == 0) sort_lock = 0;
-  __syncthreads();
   const int lane = threadIdx.x & 31;
   const int wib = threadIdx.x >> 5;
   const int w = blockIdx.x * p.warps_per_cta + wib;
   if (w >= p.rows_total) return;                         // whole warps leave; no block-wide barrier below
-  unsigned long long* keys = reinterpret_cast<unsigned long long*>(sel_smem);        // [np2], shared by the CTA
-  uint8_t* base_ptr = sel_smem + p.keys_bytes + static_cast<size_t>(wib) * p.per_warp_bytes;
-  float* cval = reinterpret_cast<float*>(base_ptr);                                  // [M] positive scores (-1 = taken)
-  uint16_t* cidx = reinterpret_cast<uint16_t*>(base_ptr + p.vals_bytes);             // [M] their columns, ascending
-  uint32_t* taken = reinterpret_cast<uint32_t*>(base_ptr + p.vals_bytes + p.idx_bytes);   // [words]
+  uint8_t* base_ptr = sel_smem + static_cast<size_t>(wib) * p.per_warp_bytes;
+  unsigned long long* keys = reinterpret_cast<unsigned long long*>(base_ptr);        // [np2] sort buffer of this warp
+  float* cval = reinterpret_cast<float*>(base_ptr + p.keys_bytes);                   // [M] positive scores (-1 = taken)
+  uint16_t* cidx = reinterpret_cast<uint16_t*>(base_ptr + p.keys_bytes + p.vals_bytes);   // [M] their columns, ascending
+  uint32_t* taken = reinterpret_cast<uint32_t*>(base_ptr + p.keys_bytes + p.vals_bytes + p.idx_bytes);   // [words]
   uint32_t* cand = taken + p.words;                                                  // [words] columns with a positive score
 
   const int bh = w / p.q_blocks;
@@ -205,22 +202,7 @@ __global__ void select_kernel(const float* __restrict__ sums, const SelParams p,
     }
     // ---- flat rows: sort what is left of the positive scores, fp64 prefix, decide per rank
     if (!stop && live > 0) {
-      // the sort buffer is shared by the warps of the CTA (flat rows are the exception): take it in turn.
-      // The holder always releases it after a bounded amount of work; the spin itself is bounded too.
-      int got = 0;
-      if (lane == 0) {
-        for (long long spin = 0; spin < (1ll << 26); ++spin) {
-          if (atomicCAS(&sort_lock, 0, 1) == 0) { got = 1; break; }
-          __nanosleep(200);
-        }
-        __threadfence_block();
-      }
-      got = __shfl_sync(0xffffffffu, got, 0);
-      if (!got) {
-        if (lane == 0 && status) atomicExch(status, 101);
-        untaken = true;
-        stop = true;
-      } else {
+      {
         int np2 = 32;
         while (np2 < M) np2 <<= 1;
         for (int t = lane; t < np2; t += 32) {
@@ -279,10 +261,6 @@ __global__ void select_kernel(const float* __restrict__ sums, const SelParams p,
         i += live;
         live = 0;
         __syncwarp();
-        if (lane == 0) {
-          __threadfence_block();
-          atomicExch(&sort_lock, 0);
-        }
       }
     }
     // ---- ranks that hold a zero score (column order).  The prefix no longer moves, so after the first of
@@ -427,27 +405,27 @@ int select_launch(const float* attn_sums, int batch, int heads, int q_blocks, in
   p.threshold = threshold; p.keep_sink = keep_sink ? 1 : 0; p.keep_recent = keep_recent ? 1 : 0;
   p.list_q_blocks = list_q_blocks; p.list_k_blocks = list_k_blocks;
   p.list_q_len = list_q_len; p.list_k_len = list_k_len;
+  p.band = band ? 1 : 0;
+  const int n_read = band ? bpc : k_blocks;        // scores stored per row = most candidates a row can have
   int np2 = 32;
-  while (np2 < k_blocks) np2 <<= 1;
+  while (np2 < n_read) np2 <<= 1;
   p.np2 = np2;
   p.words = (k_blocks + 31) / 32;
-  p.vals_bytes = (k_blocks * 4 + 15) & ~15;
-  p.idx_bytes = (k_blocks * 2 + 15) & ~15;
-  p.keys_bytes = np2 * 8;
-  p.per_warp_bytes = p.vals_bytes + p.idx_bytes + ((2 * p.words * 4 + 15) & ~15);
-  p.band = band ? 1 : 0;
+  p.vals_bytes = (n_read * 4 + 15) & ~15;
+  p.idx_bytes = (n_read * 2 + 15) & ~15;
+  p.keys_bytes = np2 * 8;                           // every warp has its own sort buffer: flat rows do not queue
+  p.per_warp_bytes = p.keys_bytes + p.vals_bytes + p.idx_bytes + ((2 * p.words * 4 + 15) & ~15);
   // 16-byte accesses to the rows of the scores and of the mask
-  const int n_read = band ? bpc : k_blocks;
   p.vec_in = (n_read % 4 == 0 && (reinterpret_cast<uintptr_t>(attn_sums) & 15) == 0) ? 1 : 0;
   p.vec_mask = (k_blocks % 16 == 0 && mask != nullptr && (reinterpret_cast<uintptr_t>(mask) & 15) == 0) ? 1 : 0;
-  int wpc = (48 * 1024 - p.keys_bytes) / p.per_warp_bytes;
+  int wpc = (72 * 1024) / p.per_warp_bytes;        // three CTAs per SM when rows are long
   wpc = wpc < 1 ? 1 : (wpc > 8 ? 8 : wpc);
   p.warps_per_cta = wpc;
   const long long rows = static_cast<long long>(batch) * heads * q_blocks;
   if (rows > 0x7fffffffLL) return XATTN_B200_ERR_LIMIT;
   p.rows_total = static_cast<int>(rows);
-  const size_t smem = static_cast<size_t>(p.keys_bytes) + static_cast<size_t>(wpc) * p.per_warp_bytes;
-  if (smem + 256 > 48 * 1024 &&
+  const size_t smem = static_cast<size_t>(wpc) * p.per_warp_bytes;
+  if (smem > 48 * 1024 &&
       cudaFuncSetAttribute(select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) !=
           cudaSuccess)
     return XATTN_B200_ERR_CUDA;
