@@ -26,7 +26,7 @@
 // (K and V as 32 KiB tiles, whole-block softmax: the shortest chain per item, for short lists), or as two
 // 64-key halves (S of half h in its own 64-column TMEM buffer, so while the softmax warpgroup works on one half
 // the tensor pipe computes the other half's S and the previous half's P.V; K and V as four 16 KiB half-tiles
-// per block: for long lists).  Both instantiations are launched; each CTA works in one of them.
+// per block: for long lists).  Every CTA picks one of the two from its own list lengths.
 // TMEM columns: [0,128) S of stream 0 (two 64-column halves in half mode), [128,256) S of stream 1,
 // [256,384) O of stream 0, [384,512) O of stream 1.
 #include <math.h>
@@ -131,17 +131,14 @@ struct Sched {
 
 // kHalf selects how a stream walks a 128-key block: as two 64-key halves with their own S buffers (softmax of
 // one half overlaps the MMAs of the other: 62 % of the dense bf16 peak on long lists) or as one block (fewer
-// instructions and barriers: better when a row lists only a handful of blocks).  Both instantiations are
-// launched; each CTA sums its own block counts in the prologue and returns at once from the instantiation that
-// is not meant for its average list length, so the choice needs no host synchronisation.
+// instructions and barriers: better when a row lists only a handful of blocks).  The kernel sums the CTA's
+// block counts while it builds the schedule and calls the body meant for its average list length, so the
+// choice needs no host synchronisation.
 constexpr int kHalfModeMinBlocks = 5;    // average listed blocks per non-empty item from which halves pay off
 template <bool kHalf>
-__global__ void __launch_bounds__(kAttnThreads, 1)
-block_sparse_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                         const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmKf,
-                         const __grid_constant__ CUtensorMap tmVf, const AttnParams p,
-                         const int32_t* __restrict__ block_idx, const int32_t* __restrict__ block_cnt,
-                         void* __restrict__ out, int* status) {
+__device__ __forceinline__ void attn_cta(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV,
+                                         const CUtensorMap& tmKf, const CUtensorMap& tmVf, const AttnParams& p,
+                                         const int32_t* __restrict__ block_idx, void* __restrict__ out, int* status) {
   // Shared memory takes nearly the whole L1, so a register spilled to local memory costs an L2 round trip:
   // the split below is the one with which ptxas reports no spill for any role of this instantiation.
 #ifdef XB_A_SM
@@ -170,12 +167,7 @@ block_sparse_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
   const int trace_role = warp < 4 ? 2 : (warp < 8 ? 3 : (warp < 12 ? 4 : (warp == 12 ? 0 : (warp == 13 ? 1 : (warp == 14 ? 5 : 6)))));
 #endif
 
-  if ((smem_u32(smem) & 1023u) != 0) {              // the swizzled tiles need 1024-byte alignment
-    if (threadIdx.x == 0 && status) atomicExch(status, static_cast<int>(kDevBadSmemAlign));
-    return;
-  }
-
-  // schedule table
+  // schedule table, built by the kernel before it picked this instantiation
   uint16_t* sch_cnt = reinterpret_cast<uint16_t*>(smem + kAttnSmemTiles + 2 * 2 * 128 * 4 + 512);
   uint16_t* sch_seq0 = sch_cnt + kSchedCap;
   uint16_t* sch_seq1 = sch_seq0 + kSchedCap;
@@ -183,36 +175,6 @@ block_sparse_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
   uint8_t* stage_base = reinterpret_cast<uint8_t*>(sch_total) + 16;     // 16-byte aligned (sch_total: 2 ints)
   const int G = gridDim.x;
   const int n_local = (p.total_items - static_cast<int>(blockIdx.x) + G - 1) / G;     // host guarantees <= kSchedCap
-  for (int i = threadIdx.x; i < n_local; i += kAttnThreads) {
-    const int c = __ldg(block_cnt + decode_item(p, blockIdx.x + i * G).row);
-    sch_cnt[i] = static_cast<uint16_t>(c > 65535 ? 65535 : c);
-  }
-  __syncthreads();
-  if (warp == 0) {
-    int running = 0, blocks = 0;
-    for (int base = 0; base < n_local; base += 32) {
-      const int i = base + lane;
-      const int c = i < n_local ? sch_cnt[i] : 0;
-      const bool ne = c > 0;
-      const unsigned bal = __ballot_sync(0xffffffffu, ne);
-      const int k = running + __popc(bal & ((1u << lane) - 1u));
-      if (ne) ((k & 1) ? sch_seq1 : sch_seq0)[k >> 1] = static_cast<uint16_t>(i);
-      running += __popc(bal);
-      blocks += c;
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) blocks += __shfl_xor_sync(0xffffffffu, blocks, o);
-    if (lane == 0) {
-      sch_total[0] = running;
-      sch_total[1] = blocks;
-    }
-  }
-  __syncthreads();
-  {
-    // which instantiation serves this CTA: the other one returns here, before touching barriers or tensor memory
-    const bool want_half = sch_total[1] >= kHalfModeMinBlocks * sch_total[0];
-    if (want_half != kHalf) return;
-  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < 2; ++s)
       for (int w = 0; w < NBAR; ++w)
@@ -903,6 +865,58 @@ block_sparse_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
   }
 }
 
+// The kernel: builds the CTA's schedule in shared memory, sums its list lengths and runs the instantiation that
+// fits them (a CTA executes only one of the two bodies, so only that one occupies its instruction cache).
+__global__ void __launch_bounds__(kAttnThreads, 1)
+block_sparse_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                         const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmKf,
+                         const __grid_constant__ CUtensorMap tmVf, const AttnParams p,
+                         const int32_t* __restrict__ block_idx, const int32_t* __restrict__ block_cnt,
+                         void* __restrict__ out, int* status) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  if ((smem_u32(smem) & 1023u) != 0) {              // the swizzled tiles need 1024-byte alignment
+    if (threadIdx.x == 0 && status) atomicExch(status, static_cast<int>(kDevBadSmemAlign));
+    return;
+  }
+  uint16_t* sch_cnt = reinterpret_cast<uint16_t*>(smem + kAttnSmemTiles + 2 * 2 * 128 * 4 + 512);
+  uint16_t* sch_seq0 = sch_cnt + kSchedCap;
+  uint16_t* sch_seq1 = sch_seq0 + kSchedCap;
+  int* sch_total = reinterpret_cast<int*>(sch_seq1 + kSchedCap);
+  const int G = gridDim.x;
+  const int n_local = (p.total_items - static_cast<int>(blockIdx.x) + G - 1) / G;     // host guarantees <= kSchedCap
+  for (int i = threadIdx.x; i < n_local; i += kAttnThreads) {
+    const int c = __ldg(block_cnt + decode_item(p, blockIdx.x + i * G).row);
+    sch_cnt[i] = static_cast<uint16_t>(c > 65535 ? 65535 : c);
+  }
+  __syncthreads();
+  if (warp == 0) {
+    int running = 0, blocks = 0;
+    for (int base = 0; base < n_local; base += 32) {
+      const int i = base + lane;
+      const int c = i < n_local ? sch_cnt[i] : 0;
+      const bool ne = c > 0;
+      const unsigned bal = __ballot_sync(0xffffffffu, ne);
+      const int k = running + __popc(bal & ((1u << lane) - 1u));
+      if (ne) ((k & 1) ? sch_seq1 : sch_seq0)[k >> 1] = static_cast<uint16_t>(i);
+      running += __popc(bal);
+      blocks += c;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) blocks += __shfl_xor_sync(0xffffffffu, blocks, o);
+    if (lane == 0) {
+      sch_total[0] = running;
+      sch_total[1] = blocks;
+    }
+  }
+  __syncthreads();
+  if (sch_total[1] >= kHalfModeMinBlocks * sch_total[0])
+    attn_cta<true>(tmQ, tmK, tmV, tmKf, tmVf, p, block_idx, out, status);
+  else
+    attn_cta<false>(tmQ, tmK, tmV, tmKf, tmVf, p, block_idx, out, status);
+}
+
 // [64 columns, rows, 2 column halves, heads, batch]: one box {64, rows, 2, 1, 1} brings `rows` x 128 columns
 // with a single TMA instruction, laid out as two 64-column swizzled halves one after the other (Q: 128 rows,
 // K/V: 64-key half tiles).
@@ -942,10 +956,8 @@ int block_sparse_attn_launch(const void* q, const void* k, const void* v, int dt
   p.causal = causal ? 1 : 0; p.is_bf16 = dtype == XATTN_B200_BF16 ? 1 : 0;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.osb = osb; p.osh = osh; p.osl = osl;
-  if (cudaFuncSetAttribute(block_sparse_attn_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem) !=
-          cudaSuccess ||
-      cudaFuncSetAttribute(block_sparse_attn_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem) !=
-          cudaSuccess)
+  if (cudaFuncSetAttribute(block_sparse_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem) !=
+      cudaSuccess)
     return XATTN_B200_ERR_CUDA;
   const long long items = static_cast<long long>(batch) * hq * p.q_blocks;
   if (items > 0x7fffffffLL) return XATTN_B200_ERR_LIMIT;
@@ -953,12 +965,8 @@ int block_sparse_attn_launch(const void* q, const void* k, const void* v, int dt
   const int sms = sm_count();
   const int grid = items < sms ? static_cast<int>(items) : sms;
   if ((items + grid - 1) / grid > kSchedCap || p.list_k_blocks > 65535) return XATTN_B200_ERR_LIMIT;
-  // both instantiations; every CTA does its work in exactly one of them (see kHalfModeMinBlocks)
-  block_sparse_attn_kernel<false><<<grid, kAttnThreads, kAttnSmem, stream>>>(tmQ, tmK, tmV, tmKf, tmVf, p, block_idx,
-                                                                             block_cnt, out, status);
-  if ((rc = launch_status())) return rc;
-  block_sparse_attn_kernel<true><<<grid, kAttnThreads, kAttnSmem, stream>>>(tmQ, tmK, tmV, tmKf, tmVf, p, block_idx,
-                                                                            block_cnt, out, status);
+  block_sparse_attn_kernel<<<grid, kAttnThreads, kAttnSmem, stream>>>(tmQ, tmK, tmV, tmKf, tmVf, p, block_idx, block_cnt,
+                                                                      out, status);
   return launch_status();
 }
 
