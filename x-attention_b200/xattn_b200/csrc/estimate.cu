@@ -16,7 +16,8 @@
 //                        sums over groups of block/S columns.  Output per (row, key block): an
 //                        un-normalised partial sum, plus the max it was taken against per (row, tile).
 //   est_rowstat_kernel   per row: combine the tiles' maxima and sums into the row's max and 1/sum
-//   est_blocksum_kernel  per (query block, key block): normalise and add the block/S rows.
+//   est_blocksum_kernel  per (query block, key block): normalise and add the block/S rows (and, when a row
+//                        spans at most eight tiles, compute the row statistics itself: no est_rowstat launch).
 #include <math.h>
 
 #include "host_common.cuh"
@@ -564,13 +565,41 @@ est_rowstat_kernel(const EstGeom g, const int* __restrict__ tile_lo, const int* 
 }
 
 // VEC consecutive key blocks per thread (4 when kb_total is a multiple of 4: one 16-byte store; they share a tile)
-template <int VEC>
+// FUSED: the query block's row statistics are computed here (eight threads per row, one (max, sum) pair each, so
+// a row costs one memory round trip) instead of being read from est_rowstat_kernel's output; for geometries whose
+// rows span at most eight column tiles.
+template <int VEC, bool FUSED>
 __global__ void __launch_bounds__(256)
 est_blocksum_kernel(const EstGeom g, const int* __restrict__ tile_lo, const int* __restrict__ tile_prefix,
                     const float* __restrict__ partial, const float2* __restrict__ mtile,
                     const float2* __restrict__ rowstat, float* __restrict__ sums) {
+  __shared__ float2 s_stat[32];                            // FUSED: (m_i, 1/l_i) of the query block's rows (rbs <= 32)
   const int qb = blockIdx.y, bh = blockIdx.z;
   const int i0 = qb * g.rbs;
+  if (FUSED) {
+    const int mt_ = i0 / kTileM;
+    const int nlo_ = __ldg(tile_lo + mt_);
+    const int ncnt_ = __ldg(tile_prefix + mt_ + 1) - __ldg(tile_prefix + mt_);
+    int rows_ = g.rows_valid - i0;
+    rows_ = rows_ > g.rbs ? g.rbs : rows_;
+    const int row = threadIdx.x >> 3, slot = threadIdx.x & 7;
+    if (row < g.rbs) {                                     // whole 8-lane groups take the branch together
+      float2 ms = make_float2(-INFINITY, 0.f);
+      if (row < rows_ && slot < ncnt_)
+        ms = mtile[(static_cast<size_t>(bh) * g.rows_total + i0 + row) * g.n_ntiles + nlo_ + slot];
+      const unsigned grp = 0xffu << (threadIdx.x & 24);    // the eight lanes of this row
+      float m = ms.x;
+      m = fmaxf(m, __shfl_xor_sync(grp, m, 1));
+      m = fmaxf(m, __shfl_xor_sync(grp, m, 2));
+      m = fmaxf(m, __shfl_xor_sync(grp, m, 4));
+      const float term = (m > -INFINITY && ms.x > -INFINITY) ? ms.y * exp2f(ms.x - m) : 0.f;
+      float l = 0.f;                                       // summed in tile order, as est_rowstat_kernel does
+#pragma unroll
+      for (int k = 0; k < 8; ++k) l += __shfl_sync(grp, term, (threadIdx.x & 24) + k);
+      if (slot == 0) s_stat[row] = make_float2(m, l > 0.f ? 1.f / l : 0.f);
+    }
+    __syncthreads();
+  }
   // band layout: only the key blocks of the query block's own chunk, [cur, cur + bpc)
   const int cur = g.band ? (g.row_off + (i0 / g.rcs) * g.rcs) / g.rbs : 0;
   const int kb_local = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
@@ -590,7 +619,7 @@ est_blocksum_kernel(const EstGeom g, const int* __restrict__ tile_lo, const int*
     rows = rows > g.rbs ? g.rbs : rows;
 #pragma unroll 2
     for (int row = 0; row < rows; ++row) {
-      const float2 st = rowstat[r0 + row];
+      const float2 st = FUSED ? s_stat[row] : rowstat[r0 + row];
       const float mx = mtile[(r0 + row) * g.n_ntiles + t].x;
       const float f = (st.y > 0.f && mx > -INFINITY) ? exp2f(mx - st.x) * st.y : 0.f;
       const float* pp = partial + (r0 + row) * g.kb_total + kb;
@@ -813,18 +842,31 @@ int estimate_launch(const void* q, const void* k, int dtype, int batch, int hq, 
 
   const long long total_rows = static_cast<long long>(batch) * hq * g.rows_total;
   if (total_rows > 0x7fffffffLL || batch * hq > 65535 || g.qb_total > 65535) return XATTN_B200_ERR_LIMIT;
-  est_rowstat_kernel<<<static_cast<int>((total_rows + 255) / 256), 256, 0, stream>>>(
-      g, tile_lo, tile_prefix, mtile, rowstat, static_cast<int>(total_rows));
-  if ((rc = launch_status())) return rc;
+  // rows that span at most eight column tiles: their statistics are computed inside est_blocksum_kernel
+  int max_tiles_per_row = g.n_ntiles;
+  // (a chunk starts at a multiple of rcs columns, so it is tile-aligned when rcs is a multiple of the tile width)
+  if (g.left_blank) max_tiles_per_row = g.rcs % g.tile_n == 0 ? g.rcs / g.tile_n : g.rcs / g.tile_n + 2;
   const int out_cols = g.band ? g.bpc : g.kb_total;
   const bool vec4 = g.kb_total % 4 == 0 && out_cols % 4 == 0 && (reinterpret_cast<uintptr_t>(attn_sums) & 15) == 0;
   const int per_row = vec4 ? out_cols / 4 : out_cols;
-  const int bt = per_row >= 256 ? 256 : ((per_row + 31) / 32) * 32;
+  // (and a query block with enough key blocks to amortise the extra round trip: measured -11 us at 32K, where a
+  // CTA sums 128 key blocks, and +10 us at 128K, where it sums 16)
+  const bool fused = max_tiles_per_row <= 8 && per_row >= 32;
+  if (!fused) {
+    est_rowstat_kernel<<<static_cast<int>((total_rows + 255) / 256), 256, 0, stream>>>(
+        g, tile_lo, tile_prefix, mtile, rowstat, static_cast<int>(total_rows));
+    if ((rc = launch_status())) return rc;
+  }
+  int bt = per_row >= 256 ? 256 : ((per_row + 31) / 32) * 32;
+  if (fused && bt < 8 * g.rbs) bt = 8 * g.rbs;           // eight threads per row for the statistics (rbs <= 32)
   const dim3 fgrid((per_row + bt - 1) / bt, g.qb_total, batch * hq);
-  if (vec4)
-    est_blocksum_kernel<4><<<fgrid, bt, 0, stream>>>(g, tile_lo, tile_prefix, partial, mtile, rowstat, attn_sums);
-  else
-    est_blocksum_kernel<1><<<fgrid, bt, 0, stream>>>(g, tile_lo, tile_prefix, partial, mtile, rowstat, attn_sums);
+  if (vec4) {
+    if (fused) est_blocksum_kernel<4, true><<<fgrid, bt, 0, stream>>>(g, tile_lo, tile_prefix, partial, mtile, rowstat, attn_sums);
+    else est_blocksum_kernel<4, false><<<fgrid, bt, 0, stream>>>(g, tile_lo, tile_prefix, partial, mtile, rowstat, attn_sums);
+  } else {
+    if (fused) est_blocksum_kernel<1, true><<<fgrid, bt, 0, stream>>>(g, tile_lo, tile_prefix, partial, mtile, rowstat, attn_sums);
+    else est_blocksum_kernel<1, false><<<fgrid, bt, 0, stream>>>(g, tile_lo, tile_prefix, partial, mtile, rowstat, attn_sums);
+  }
   return launch_status();
 }
 
