@@ -348,9 +348,11 @@ def run_gpu_arm(args):
             config=_config(w, chunk, n), clocks=clocks,
             e2e=dict(value=e2e_value, unit=UNIT, ms_per_step=ms_e2e, h2d_bytes_per_step=bi, d2h_bytes_per_step=bo,
                      host_cores_bound=len(numa_cores) if numa_cores else None),
-            gpu_launches=(6 if w.seq_len >= 131072 else 5) * args.steps,
+            # est_setup, est_gemm(_pair), [est_rowstat], est_blocksum, select, block_sparse_attn; the row statistics
+            # are a launch of their own except where est_blocksum computes them (the 32K workload)
+            gpu_launches=(5 if args.workload == "llama3_8b_32k" else 6) * args.steps,
             kernels_per_step=["est_setup_kernel", "est_gemm_pair_kernel | est_gemm_kernel",
-                              "est_rowstat_kernel (128K only)", "est_blocksum_kernel",
+                              "est_rowstat_kernel (not at 32K)", "est_blocksum_kernel",
                               "select_kernel", "block_sparse_attn_kernel"],
             phases_ms=dict(estimate=ph[0], select=ph[1], attend=ph[2]),
             block_density=density, roofline=roofline, attention_dense_mask=dense, cpu_baseline=cpu_baseline,
