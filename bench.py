@@ -36,8 +36,8 @@ import torch  # noqa: E402
 METRIC = "prefill_attention_effective_tflops"
 UNIT = "TFLOP/s (dense-equivalent, 4*Lq*Lk*D*Hq/2 causal)"
 # dram__bytes_read.sum + dram__bytes_write.sum of one block_sparse_attn_kernel launch, from the ncu capture that
-# profiles/block_sparse_attn_kernel_llama3_8b_32k.md summarises (405.6 MB + 233.5 MB); other workloads: not captured
-NCU_ATTENTION_TRAFFIC_BYTES = {"llama3_8b_32k": 639_147_008}
+# profiles/block_sparse_attn_kernel_llama3_8b_32k.md summarises (406.4 MB + 233.4 MB); other workloads: not captured
+NCU_ATTENTION_TRAFFIC_BYTES = {"llama3_8b_32k": 639_788_544}
 DEFAULT_WORKLOAD = "llama3_8b_32k"
 
 
@@ -46,6 +46,33 @@ def effective_flops(w, heads=None, q_rows=None) -> float:
     lq = w.seq_len if q_rows is None else q_rows
     f = 4.0 * lq * w.seq_len * w.head_dim * hq
     return f * 0.5 if w.causal else f
+
+
+def estimate_executed_flops(w, chunk, torch_branch=True):
+    """FLOPs of the estimate GEMM as executed: 2 * 128 * tile_n * (S*D) per visible tile (csrc/estimate.cu picks
+    the visible column tiles of every 128-row tile of the stride-reshaped problem; same bounds here)."""
+    S, D, L = w.stride, w.head_dim, w.seq_len
+    lp = -(-L // chunk) * chunk
+    rows = lp // S
+    rcs = chunk // S
+    k_pad = lp - L
+    left_blank = w.causal and torch_branch and k_pad == 0
+    tile_n = 128 if (left_blank and rcs <= 128) else 256
+    rows_valid = rows - k_pad // S
+    cols_valid = rows - k_pad // S
+    tiles = 0
+    for mt in range((rows + 127) // 128):
+        i0, i1 = mt * 128, min((mt + 1) * 128, rows, rows_valid)
+        if i1 <= i0:
+            continue
+        if not w.causal:
+            lo, hi = 0, rows - 1
+        else:
+            lo = (i0 // rcs) * rcs if left_blank else 0
+            hi = min(i1 - 1, cols_valid - 1)
+        if hi >= lo:
+            tiles += hi // tile_n - lo // tile_n + 1
+    return 2.0 * 128 * tile_n * S * D * tiles * w.hq
 
 
 def measured_peaks():
@@ -294,6 +321,20 @@ def run_gpu_arm(args):
                     peak_source=peaks["source"],
                     executed_flops_per_launch=f_att, selected_blocks=n_sel)
 
+    # every phase against its roofline: the two tensor-core phases against the measured dense bf16 peak, the
+    # selection against the measured HBM copy bandwidth (bytes: the block sums it reads + the lists it writes)
+    band = ops.band_applies(w.seq_len, chunk, w.causal)
+    f_est = estimate_executed_flops(w, chunk)
+    sel_bytes = 4.0 * w.hq * g["qb"] * (g["bpc"] if band else g["kb"]) + 4.0 * n_sel + 4.0 * w.hq * qb
+    phase_rooflines = dict(
+        estimate=dict(bound="tensor", executed_flops=f_est, achieved=f_est / (ph[0] * 1e-3) / 1e12, unit="TFLOP/s",
+                      peak=peaks["bf16"], frac=f_est / (ph[0] * 1e-3) / 1e12 / peaks["bf16"]),
+        select=dict(bound="hbm", bytes=sel_bytes, achieved=sel_bytes / (ph[1] * 1e-3) / 1e9, unit="GB/s",
+                    peak=peaks["hbm"], frac=sel_bytes / (ph[1] * 1e-3) / 1e9 / peaks["hbm"],
+                    note="a 13-30 us phase: launch latency and one dependent memory round trip per row, not bandwidth"),
+        attend=dict(bound="tensor", executed_flops=f_att, achieved=att_tflops, unit="TFLOP/s", peak=peaks["bf16"],
+                    frac=att_tflops / peaks["bf16"]))
+
     # the same attention kernel on a dense causal mask (long block lists): what the inner loop sustains when the
     # per-item prologue/epilogue no longer dominates.  Rank 0 only, a few launches.
     dense = None
@@ -355,7 +396,8 @@ def run_gpu_arm(args):
                               "est_rowstat_kernel (not at 32K)", "est_blocksum_kernel",
                               "select_kernel", "block_sparse_attn_kernel"],
             phases_ms=dict(estimate=ph[0], select=ph[1], attend=ph[2]),
-            block_density=density, roofline=roofline, attention_dense_mask=dense, cpu_baseline=cpu_baseline,
+            block_density=density, roofline=roofline, phase_rooflines=phase_rooflines, attention_dense_mask=dense,
+            cpu_baseline=cpu_baseline,
         )
         print(json.dumps(line), flush=True)
     if dist is not None:
