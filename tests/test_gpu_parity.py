@@ -15,6 +15,14 @@ GOLD = os.path.join(os.path.dirname(__file__), "golden")
 DEV = "cuda"
 
 
+def _assert_same_up_to_body_choice(a, b, msg=None):
+    """Two ways of cutting the same prefill into kernel launches select the same blocks, but a CTA picks its
+    attention body (whole blocks / half blocks) from the lists it happens to hold, and the two bodies add in
+    a different order and round P against different running maxima: outputs agree to a few units of the last
+    place of the 16-bit format (the bar against the oracle is 2e-2 max-abs)."""
+    torch.testing.assert_close(a.float(), b.float(), rtol=2.0 ** -6, atol=2.0 ** -8, msg=msg)
+
+
 def _load(name):
     z = np.load(os.path.join(GOLD, name))
     return z, json.loads(str(z["specs"]))
@@ -218,7 +226,7 @@ def test_long_lists_take_the_half_block_path(causal, density, hq, hkv, L):
     qb = (L + 127) // 128
     mask = _random_block_mask(g, hq, qb, qb, causal, density)
     idx, cnt = ops.mask_to_lists(mask.to(DEV), L, L, causal)
-    assert float(cnt.float().mean()) >= 5          # the kernel's switch-over point
+    assert float(cnt.float().mean()) >= 5          # well above the kernel's switch-over point (3.5)
     out = ops.block_sparse_attention(q.to(DEV), k.to(DEV), v.to(DEV), idx, cnt, causal).float().cpu()
     ref = orc.block_sparse_attention_oracle(q, k, v, mask, causal)
     err = (out - ref).abs()
@@ -389,7 +397,7 @@ def test_prefill_dense_threshold_one_matches_sdpa():
 
 
 def test_host_pipeline_equals_device_call():
-    """Xattention_prefill_host (pinned host tensors, kv groups streamed over PCIe) gives the bits of the
+    """Xattention_prefill_host (pinned host tensors, kv groups streamed over PCIe) gives the result of the
     device call."""
     import xattn_b200
     from xattn_b200 import synth
@@ -399,7 +407,7 @@ def test_host_pipeline_equals_device_call():
         out = xattn_b200.Xattention_prefill_host(q.pin_memory(), k.pin_memory(), v.pin_memory(), 8, threshold=0.9,
                                                  chunk_size=2048, groups_per_step=gps)
         assert not out.is_cuda and out.shape == q.shape
-        assert torch.equal(out, ref.cpu())
+        _assert_same_up_to_body_choice(out, ref.cpu())
 
 
 def test_head_shards_concatenate_to_the_full_result():
@@ -414,12 +422,12 @@ def test_head_shards_concatenate_to_the_full_result():
     for world in (2, 4):
         parts = [prefill_sharded(dq, dk, dv, xattn_b200.Xattention_prefill, world, r, threshold=thr, stride=8,
                                  chunk_size=2048) for r in range(world)]
-        assert torch.equal(torch.cat(parts, dim=1), full)
+        _assert_same_up_to_body_choice(torch.cat(parts, dim=1), full)
 
 
 def test_query_chunk_shards_equal_the_full_call():
     """Causal prefill cut into query chunks (as dealt to ranks for very long sequences), each computed
-    against the keys up to its own end, reproduces the single call bit for bit."""
+    against the keys up to its own end, reproduces the single call."""
     import xattn_b200
     from xattn_b200 import synth
     from xattn_b200.sharding import prefill_query_chunk_sharded
@@ -431,7 +439,7 @@ def test_query_chunk_shards_equal_the_full_call():
             parts = prefill_query_chunk_sharded(dq, dk, dv, xattn_b200.Xattention_prefill, world, r, 2048,
                                                 threshold=0.9, stride=16)
             for c, o in parts.items():
-                assert torch.equal(o, full[:, :, c * 2048:(c + 1) * 2048]), (world, r, c)
+                _assert_same_up_to_body_choice(o, full[:, :, c * 2048:(c + 1) * 2048], msg=str((world, r, c)))
 
 
 def test_prefill_against_a_longer_key_cache():

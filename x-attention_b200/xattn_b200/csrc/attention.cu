@@ -22,7 +22,7 @@
 //
 // Lists are walked from the last entry (the diagonal block when causal, which usually holds the row
 // maximum) to the first, so the running maximum settles at the first block and O is rarely rescaled.
-// The kernel is a template over how a stream walks a 128-key block (see kHalfModeMinBlocks): as one block
+// The kernel is a template over how a stream walks a 128-key block (see kHalfModeMinBlocksX2): as one block
 // (K and V as 32 KiB tiles, whole-block softmax: the shortest chain per item, for short lists), or as two
 // 64-key halves (S of half h in its own 64-column TMEM buffer, so while the softmax warpgroup works on one half
 // the tensor pipe computes the other half's S and the previous half's P.V; K and V as four 16 KiB half-tiles
@@ -134,7 +134,10 @@ struct Sched {
 // instructions and barriers: better when a row lists only a handful of blocks).  The kernel sums the CTA's
 // block counts while it builds the schedule and calls the body meant for its average list length, so the
 // choice needs no host synchronisation.
-constexpr int kHalfModeMinBlocks = 5;    // average listed blocks per non-empty item from which halves pay off
+// twice the average number of listed blocks per non-empty item from which the half-block body pays off
+// (random masks with n blocks per row, 16 heads x 16K: n=2 full 457 / half 397 TFLOP/s, n=3 528 / 522,
+// n=4 577 / 637, n=8 659 / 799, n=24 718 / 955)
+constexpr int kHalfModeMinBlocksX2 = 7;
 template <bool kHalf>
 __device__ __forceinline__ void attn_cta(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV,
                                          const CUtensorMap& tmKf, const CUtensorMap& tmVf, const AttnParams& p,
@@ -911,7 +914,7 @@ block_sparse_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
     }
   }
   __syncthreads();
-  if (sch_total[1] >= kHalfModeMinBlocks * sch_total[0])
+  if (2 * sch_total[1] >= kHalfModeMinBlocksX2 * sch_total[0])
     attn_cta<true>(tmQ, tmK, tmV, tmKf, tmVf, p, block_idx, out, status);
   else
     attn_cta<false>(tmQ, tmK, tmV, tmKf, tmVf, p, block_idx, out, status);
