@@ -382,7 +382,8 @@ __device__ __forceinline__ void attn_cta(const CUtensorMap& tmQ, const CUtensorM
           mma_commit(bar(s, H_EMPTY));
           mma_commit(bar(s, S_FULL));
           if (j == n - 1) mma_commit(bar(s, Q_EMPTY));
-          // O += P V
+          // O += P V, in two steps: keys 0-63 as soon as their half of P is written, so that this half of the
+          // product runs while the softmax warpgroup still exponentiates keys 64-127
           if (!mbar_wait(bar(s, P_READY), bc & 1, abort_flag)) { ok = false; break; }
           if (!mbar_wait(bar(s, H_FULL + 2), bc & 1, abort_flag)) { ok = false; break; }
           if (j == 0 && !mbar_wait(bar(s, O_EMPTY), (m & 1) ^ 1, abort_flag)) { ok = false; break; }
@@ -390,7 +391,11 @@ __device__ __forceinline__ void attn_cta(const CUtensorMap& tmQ, const CUtensorM
           XB_TRACE_EV(0x22, bc);
           mma_ts(od, sd, dv[0], idesc_pv, j > 0 ? 1u : 0u);
 #pragma unroll
-          for (int k = 1; k < 8; ++k) mma_ts(od, sd + k * 8, dv[k], idesc_pv, 1u);
+          for (int k = 1; k < 4; ++k) mma_ts(od, sd + k * 8, dv[k], idesc_pv, 1u);
+          if (!mbar_wait(bar(s, P_READY + 1), bc & 1, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+#pragma unroll
+          for (int k = 4; k < 8; ++k) mma_ts(od, sd + k * 8, dv[k], idesc_pv, 1u);
           mma_commit(bar(s, H_EMPTY + 2));
           if (j == n - 1) mma_commit(bar(s, O_FULL));
         }
@@ -555,7 +560,7 @@ __device__ __forceinline__ void attn_cta(const CUtensorMap& tmQ, const CUtensorM
     const uint32_t ts = tmem_base + s * 128 + lane_bits;          // S / P of this stream, this row
     const uint32_t tmem_o = tmem_base + 256 + s * 128 + lane_bits;
     const int k_off = p.k_len - p.q_len;
-    const uint32_t s_full = bar(s, S_FULL), p_ready = bar(s, P_READY);
+    const uint32_t s_full = bar(s, S_FULL);
     const int n_items = sch.n_seq[s];
     uint32_t bc = 0;
     bool ok = true;
@@ -700,10 +705,21 @@ __device__ __forceinline__ void attn_cta(const CUtensorMap& tmQ, const CUtensorM
             tc_wait_ld();
             if (c2 == 0) tmem_ld32(ts + 64, va);
             chunk(vb, 2 * c2 + 1);
+            if (c2 == 0) {
+              // P of keys 0-63 is complete: their half of P.V may start
+              tc_wait_st();
+              tc_fence_before();
+              mbar_arrive(bar(s, P_READY));
+            }
           }
         }
 #pragma unroll 1
         for (int c4 = masked ? 0 : 4; c4 < 4; ++c4) {
+          if (c4 == 2) {
+            tc_wait_st();
+            tc_fence_before();
+            mbar_arrive(bar(s, P_READY));
+          }
           uint32_t pk[16];
           if ((cls_none >> c4) & 1u) {
 #pragma unroll
@@ -748,7 +764,7 @@ __device__ __forceinline__ void attn_cta(const CUtensorMap& tmQ, const CUtensorM
         if (j == n - 1) s_l[(s * 2 + (m & 1)) * 128 + r] = l;   // read by the epilogue once this item's last P.V is done
         tc_wait_st();
         tc_fence_before();
-        mbar_arrive(p_ready);
+        mbar_arrive(bar(s, P_READY + 1));
         if (threadIdx.x == (s << 7)) XB_TRACE_EV(0x33, bc);
       }
       it = nit; n = nn; win = nwin;
