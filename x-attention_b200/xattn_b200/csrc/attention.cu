@@ -135,8 +135,8 @@ struct Sched {
 // block counts while it builds the schedule and calls the body meant for its average list length, so the
 // choice needs no host synchronisation.
 // twice the average number of listed blocks per non-empty item from which the half-block body pays off
-// (random masks with n blocks per row, 16 heads x 16K: n=2 full 457 / half 397 TFLOP/s, n=3 528 / 522,
-// n=4 577 / 637, n=8 659 / 799, n=24 718 / 955)
+// (random masks with n blocks per row, 16 heads x 16K: n=2 full 473 / half 391 TFLOP/s, n=3 549 / 518,
+// n=4 603 / 629, n=8 709 / 797, n=24 801 / 945)
 constexpr int kHalfModeMinBlocksX2 = 7;
 template <bool kHalf>
 __device__ __forceinline__ void attn_cta(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV,
