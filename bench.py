@@ -36,8 +36,8 @@ import torch  # noqa: E402
 METRIC = "prefill_attention_effective_tflops"
 UNIT = "TFLOP/s (dense-equivalent, 4*Lq*Lk*D*Hq/2 causal)"
 # dram__bytes_read.sum + dram__bytes_write.sum of one block_sparse_attn_kernel launch, from the ncu capture that
-# profiles/block_sparse_attn_kernel_llama3_8b_32k.md summarises (406.4 MB + 233.4 MB); other workloads: not captured
-NCU_ATTENTION_TRAFFIC_BYTES = {"llama3_8b_32k": 639_788_544}
+# profiles/block_sparse_attn_kernel_llama3_8b_32k.md summarises (406.9 MB + 233.7 MB); other workloads: not captured
+NCU_ATTENTION_TRAFFIC_BYTES = {"llama3_8b_32k": 640_664_576}
 DEFAULT_WORKLOAD = "llama3_8b_32k"
 
 
