@@ -605,10 +605,12 @@ def test_chunk_band_layout_equals_the_dense_one(name, L, Lq, chunk):
         rows = slice(c * g["bpc"], (c + 1) * g["bpc"])
         rebuilt[:, :, rows, cur:cur + g["bpc"]] = band[:, :, rows]
     assert torch.equal(rebuilt, dense)
-    for thr in (0.9, torch.linspace(0.5, 1.0, q.shape[1])):
-        m0, i0, c0 = ops.select_blocks(dense, g["bpc"], g["block_offset"], thr, True, True, list_shape=(Lq, L))
-        m1, i1, c1 = ops.select_blocks(band, g["bpc"], g["block_offset"], thr, True, True, list_shape=(Lq, L),
-                                       band_k_blocks=g["kb"])
+    for thr, sink, recent in ((0.9, False, False), (torch.linspace(0.5, 1.0, q.shape[1]), False, False),
+                              (0.7, True, True), (0.0, False, True), (1.0, True, False)):
+        m0, i0, c0 = ops.select_blocks(dense, g["bpc"], g["block_offset"], thr, True, True, sink, recent,
+                                       list_shape=(Lq, L))
+        m1, i1, c1 = ops.select_blocks(band, g["bpc"], g["block_offset"], thr, True, True, sink, recent,
+                                       list_shape=(Lq, L), band_k_blocks=g["kb"])
         assert torch.equal(m0, m1) and torch.equal(c0, c1)
         valid = torch.arange(i0.shape[-1], device=DEV)[None, None, None, :] < c0[..., None]
         assert torch.equal(i0[valid], i1[valid])
