@@ -132,7 +132,8 @@ def rope_inputs(spec):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--rope-only", action="store_true", help="only (re)generate the rotary-embedding fixture")
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("XATTN_REFERENCE"), required="XATTN_REFERENCE" not in os.environ,
+                    help="checkout of mit-han-lab/x-attention (or set XATTN_REFERENCE)")
     ap.add_argument("--triton", action="store_true", help="also (re)generate the Triton-interpreter fixtures")
     args = ap.parse_args()
     if args.triton:
