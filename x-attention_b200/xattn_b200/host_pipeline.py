@@ -62,7 +62,7 @@ def group_slices(hq: int, hkv: int, groups_per_step: int = 1):
     return out
 
 
-def plan_steps(hq: int, hkv: int, groups_per_step: int = 1, q_splits: int = 2):
+def plan_steps(hq: int, hkv: int, groups_per_step: int = 1, q_splits: int = 1):
     """Steps of the host pipeline: [(q0, q1, k0, k1, first_of_slice, last_of_slice)].  A slice is `groups_per_step`
     whole kv groups (its K/V are copied with its first step); the query heads of a slice that holds ONE kv head
     run in `q_splits` steps when that divides them.  A slice with several kv heads is never split: the kernels
@@ -80,7 +80,7 @@ def Xattention_prefill_host(query_states: torch.Tensor, key_states: torch.Tensor
                             stride, norm=1, threshold: Union[float, torch.Tensor] = 0.8, block_size=128,
                             causal=True, chunk_size=None, keep_sink=False, keep_recent=False,
                             device: Optional[torch.device] = None, out: Optional[torch.Tensor] = None,
-                            groups_per_step: int = 1, q_splits: int = 2) -> torch.Tensor:
+                            groups_per_step: int = 1, q_splits: int = 1) -> torch.Tensor:
     """Same computation as Xattention_prefill (xattn/src/Xattention.py:302-402) for host tensors.
 
     query_states [1,Hq,L,D], key/value_states [1,Hkv,L,D] on the CPU (pin them: pageable memory makes the
@@ -103,7 +103,9 @@ def Xattention_prefill_host(query_states: torch.Tensor, key_states: torch.Tensor
     band = ops.band_applies(Lk, chunk_size, bool(causal))
     slices = group_slices(Hq, Hkv, groups_per_step)
     nk = slices[0][3] - slices[0][2]
-    # smaller steps shorten what cannot overlap: the first step's input copy and the last step's output copy
+    # smaller steps shorten what cannot overlap (the first step's input copy, the last step's output copy) but make
+    # more, shorter copies: on a PCIe 5 x16 link one kv group per step measured best (8.93 ms at 32K; two steps per
+    # group 9.06, four 9.76, two groups per step 9.4)
     steps = plan_steps(Hq, Hkv, groups_per_step, q_splits)
     nq = max(st[1] - st[0] for st in steps)
     with torch.cuda.device(dev):
