@@ -117,11 +117,24 @@ __global__ void est_setup_kernel(EstGeom g, int* __restrict__ tile_lo, int* __re
   }
 }
 
+// Tile number -> (batch*head, row-tile group, column tile).  With `interleave` > 1 (the query heads per kv head)
+// the heads of a kv group take the same (row, column) tile one after the other, so that the K tile they share is
+// read from DRAM once and found in L2 by the other heads: it matters when the kernel streams its operands from
+// HBM (128-column tiles), where K otherwise came from DRAM about twice.
 __device__ __forceinline__ void decode_tile(int n_groups, const int* __restrict__ tile_lo,
                                             const int* __restrict__ tile_prefix, int tiles_per_head, int tile,
-                                            int& bh, int& mt, int& nt) {
-  bh = tile / tiles_per_head;
-  const int rem = tile - bh * tiles_per_head;
+                                            int& bh, int& mt, int& nt, int interleave = 1) {
+  int rem;
+  if (interleave > 1) {
+    const int hg = tile % interleave;                  // head inside its kv group
+    const int t2 = tile / interleave;
+    const int bkv = t2 / tiles_per_head;               // batch * kv heads + kv head
+    rem = t2 - bkv * tiles_per_head;
+    bh = bkv * interleave + hg;
+  } else {
+    bh = tile / tiles_per_head;
+    rem = tile - bh * tiles_per_head;
+  }
   int lo = 0, hi = n_groups;     // find mt with prefix[mt] <= rem < prefix[mt+1]
   while (hi - lo > 1) {
     const int mid = (lo + hi) >> 1;
@@ -262,6 +275,7 @@ est_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const int total_tiles = tiles_per_head * g.batch * g.hq;
   const int k_steps = g.S * g.d_chunks;
   const int group = g.hq / g.hkv;
+  const int interleave = g.tile_n == 128 ? group : 1;      // streaming case only: see decode_tile
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (one thread)
@@ -269,7 +283,7 @@ est_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       uint32_t it = 0;
       for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
         int bh, mt, nt;
-        decode_tile(g.n_mtiles, tile_lo, tile_prefix, tiles_per_head, tile, bh, mt, nt);
+        decode_tile(g.n_mtiles, tile_lo, tile_prefix, tiles_per_head, tile, bh, mt, nt, interleave);
         const int b = bh / g.hq, h = bh - b * g.hq;
         for (int ks = 0; ks < k_steps; ++ks, ++it) {
           const int s = it % n_stages;
@@ -323,7 +337,7 @@ est_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     uint32_t local_tile = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local_tile) {
       int bh, mt, nt;
-      decode_tile(g.n_mtiles, tile_lo, tile_prefix, tiles_per_head, tile, bh, mt, nt);
+      decode_tile(g.n_mtiles, tile_lo, tile_prefix, tiles_per_head, tile, bh, mt, nt, interleave);
       const uint32_t acc = local_tile & 1;
       const uint32_t acc_ph = (local_tile >> 1) & 1;
       const int i = mt * kTileM + r;
