@@ -3,9 +3,11 @@
  *
  * Every entry point takes plain pointers and sizes, launches on the CUDA stream it is given and
  * returns an int status (0 = ok, see xattn_b200_error_string).  Nothing here synchronises the
- * stream, throws, or keeps state between calls.  Unless stated otherwise every pointer is a
- * device pointer on the current device; the library allocates no device memory: scratch is passed
- * in by the caller, sized by the *_workspace_bytes functions.
+ * stream or throws.  Unless stated otherwise every pointer is a device pointer on the current
+ * device; the library allocates no device memory: scratch is passed in by the caller, sized by the
+ * *_workspace_bytes functions.  No entry point keeps state between calls, except
+ * xattn_b200_estimate_static, whose scratch is a fixed array inside the library that all of its
+ * calls share (see there), and the diagnostic launch counter.
  *
  * File:line citations name the reference interface (mit-han-lab/x-attention) each entry replaces.
  *
@@ -54,6 +56,10 @@ extern "C" {
 
 int xattn_b200_version(void);
 const char* xattn_b200_error_string(int code);
+
+/* Number of kernel launches the library has issued in this process so far (all entry points, all devices).
+ * A diagnostic counter for benchmarks and tests; no counterpart in the reference.  Host function. */
+unsigned long long xattn_b200_launch_count(void);
 
 /* Default estimate chunk of Xattention_prefill (xattn/src/Xattention.py:322-331). */
 int xattn_b200_default_chunk_size(int k_len);

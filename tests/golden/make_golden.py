@@ -9,6 +9,9 @@ Nothing under tests/ reads the reference at test time: the tests replay these fi
 The reference needs two shims to import/run without a GPU (none of its files is changed):
   * a stub module ``block_sparse_attn`` (imported unconditionally at xattn/src/Xattention.py:10),
   * ``Tensor.to("cuda")`` made a no-op (hard-coded at xattn/src/Xattention.py:43,47,185,251).
+The attention fixture comes from xattn/src/Flexprefill.py:12-44 (torch_block_wise_attention), the reference's own
+statement of causal block-sparse attention; that module imports triton and flash_attn at load time, so both must
+be importable where the script runs (no GPU needed).
 For the Triton-semantics fixtures the reference's Triton kernels are run by Triton's CPU
 interpreter (TRITON_INTERPRET=1) with ``torch.cuda.get_device_properties`` faked to a name
 containing "100" (gate at xattn/src/Xattention.py:57-63).
@@ -129,9 +132,71 @@ def rope_inputs(spec):
     return q, k, emb.cos().to(dt), emb.sin().to(dt)
 
 
+# block-sparse causal attention as the reference's own baseline file states it
+# (xattn/src/Flexprefill.py:12-44, torch_block_wise_attention): MHA, q_len == k_len, causal
+ATTENTION_CASES = [
+    dict(length=512, heads=3, dtype="bf16", density=0.4, seed=8001),
+    dict(length=1000, heads=2, dtype="bf16", density=0.3, seed=8002),      # ragged last block
+    dict(length=1536, heads=2, dtype="bf16", density=0.25, seed=8003),
+    dict(length=640, heads=2, dtype="fp16", density=0.5, seed=8004),
+    dict(length=1280, heads=4, dtype="bf16", density=0.0, seed=8005),      # sink + diagonal only
+]
+ATTENTION_COL_STEP = 4        # every 4th output column is stored, plus the sum of each full output row
+
+
+def attention_inputs(spec):
+    """q, k, v [1,H,L,128] rounded to the case's 16-bit dtype, and a causal block mask [1,H,nb,nb] that keeps the
+    sink block, the diagonal and a random `density` of the rest; shared with the tests."""
+    import torch
+    dt = {"bf16": torch.bfloat16, "fp16": torch.float16}[spec["dtype"]]
+    g = torch.Generator().manual_seed(spec["seed"])
+    H, L = spec["heads"], spec["length"]
+    q = torch.randn(1, H, L, 128, generator=g).to(dt)
+    k = torch.randn(1, H, L, 128, generator=g).to(dt)
+    v = torch.randn(1, H, L, 128, generator=g).to(dt)
+    nb = (L + 127) // 128
+    m = torch.rand(1, H, nb, nb, generator=g) < spec["density"]
+    m[..., 0] = True
+    m |= torch.eye(nb, dtype=torch.bool)
+    m &= torch.tril(torch.ones(nb, nb, dtype=torch.bool))
+    return q, k, v, m
+
+
+def make_attention_fixture(path):
+    """Outputs of the reference's torch_block_wise_attention (fp32, on the fp32 upcast of the rounded inputs)."""
+    import numpy as np
+    import torch
+    from xattn.src.Flexprefill import torch_block_wise_attention
+    out = {}
+    specs = []
+    for i, spec in enumerate(ATTENTION_CASES):
+        q, k, v, m = attention_inputs(spec)
+        H, L = spec["heads"], spec["length"]
+        nb = m.shape[-1]
+        # the reference takes flat block indices row*nb+col, one list length for all heads: shorter lists are
+        # filled up with repeats of block (0,0), which every list holds anyway
+        flat = [(m[0, h].reshape(-1).nonzero().flatten()) for h in range(H)]
+        width = max(int(f.numel()) for f in flat)
+        block_idx = torch.zeros(1, H, width, dtype=torch.long)
+        for h, f in enumerate(flat):
+            block_idx[0, h, : f.numel()] = f
+        o = torch_block_wise_attention(q.float().transpose(1, 2), k.float().transpose(1, 2),
+                                       v.float().transpose(1, 2), block_idx, 128)       # [1,L,H,D]
+        o = o.transpose(1, 2).contiguous()                                              # [1,H,L,D]
+        chk = float(q.double().sum() + 3.0 * k.double().sum() + 5.0 * v.double().sum())
+        out[f"out_{i}"] = o[..., ::ATTENTION_COL_STEP].contiguous().numpy()
+        out[f"rowsum_{i}"] = o.double().sum(-1).numpy()
+        out[f"mask_{i}"] = np.packbits(m.reshape(-1).numpy())
+        specs.append(dict(spec, checksum=chk, mask_shape=list(m.shape), col_step=ATTENTION_COL_STEP))
+        print("attention", i, spec, "blocks %d" % int(m.sum()))
+    out["specs"] = np.array(json.dumps(specs))
+    np.savez_compressed(path, **out)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--rope-only", action="store_true", help="only (re)generate the rotary-embedding fixture")
+    ap.add_argument("--attention-only", action="store_true", help="only (re)generate the attention fixture")
     ap.add_argument("--reference", default=os.environ.get("XATTN_REFERENCE"), required="XATTN_REFERENCE" not in os.environ,
                     help="checkout of mit-han-lab/x-attention (or set XATTN_REFERENCE)")
     ap.add_argument("--triton", action="store_true", help="also (re)generate the Triton-interpreter fixtures")
@@ -156,6 +221,10 @@ def main():
     torch.Tensor.to = _to
     from xattn.src.Xattention import xattn_estimate
     from xattn.src.utils import find_blocks_chunked
+
+    make_attention_fixture(os.path.join(HERE, "attention_blockwise.npz"))
+    if args.attention_only:
+        return
 
     # rotary embedding: the reference's own function on the same inputs; 16-bit values stored as their bits
     from xattn.src.load_llama import apply_rotary_pos_emb

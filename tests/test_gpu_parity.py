@@ -7,7 +7,7 @@ import numpy as np
 import pytest
 import torch
 
-from make_golden import case_inputs
+from make_golden import attention_inputs, case_inputs
 from oracle import xattn_oracle as orc
 
 pytestmark = pytest.mark.gpu
@@ -214,6 +214,22 @@ def test_block_sparse_attention_vs_oracle(causal, dtype, hq, hkv, lq, lk):
     assert err.max() < OUT_MAX_ABS and err.mean() < OUT_MEAN_ABS, (err.max(), err.mean())
 
 
+def test_block_sparse_attention_vs_reference_blockwise_fixture():
+    """The attention kernel against outputs of the reference's own torch_block_wise_attention
+    (xattn/src/Flexprefill.py:12-44) stored in tests/golden/attention_blockwise.npz."""
+    from xattn_b200 import ops
+    z, specs = _load("attention_blockwise.npz")
+    for i, spec in enumerate(specs):
+        q, k, v, m = attention_inputs(spec)
+        L = spec["length"]
+        idx, cnt = ops.mask_to_lists(m.to(DEV), L, L, True)
+        out = ops.block_sparse_attention(q.to(DEV), k.to(DEV), v.to(DEV), idx, cnt, True).float().cpu()
+        err = (out[..., :: spec["col_step"]] - torch.from_numpy(z[f"out_{i}"])).abs()
+        assert err.max() < OUT_MAX_ABS and err.mean() < OUT_MEAN_ABS, (spec, err.max(), err.mean())
+        rs = (out.double().sum(-1) - torch.from_numpy(z[f"rowsum_{i}"])).abs()
+        assert rs.max() < 128 * OUT_MEAN_ABS, (spec, rs.max())
+
+
 @pytest.mark.parametrize("causal,density,hq,hkv,L", [(True, 1.0, 2, 1, 4096), (False, 0.5, 2, 2, 3072), (True, 0.3, 4, 2, 5000)])
 def test_long_lists_take_the_half_block_path(causal, density, hq, hkv, L):
     """Rows that list many blocks run through the half-block instantiation of the kernel (each 128-key block
@@ -349,11 +365,76 @@ def _check_workload(q, k, v, stride, threshold, chunk, causal, sample_rows=None)
 
 
 def test_llama_32k_full_length_one_kv_group():
-    """BASELINE configs[1] at its real length (32768, S=8, chunk 16384) on one kv group (4 query heads);
+    """The llama3_8b_32k workload at its real length (32768, S=8, chunk 16384) on one kv group (4 query heads);
     outputs checked on 12 query blocks spread over the sequence."""
     from xattn_b200 import synth
     q, k, v, w = synth.make_inputs("llama3_8b_32k", seed=1, heads_limit=1)
     _check_workload(q, k, v, w.stride, w.threshold, w.chunk_size, True, sample_rows=[0, 1, 7, 31, 64, 100, 127, 128, 129, 200, 254, 255])
+
+
+def test_llama_128k_full_length_two_query_heads():
+    """The llama3_8b_128k workload at its real length (131072, S=16, default chunk 2048: 64 chunks, 1024 key
+    blocks per row, the single-CTA streaming estimate and the chunk-band layout) on two query heads of one kv
+    group: masks over all rows, outputs on 12 query blocks."""
+    from xattn_b200 import synth
+    q, k, v, w = synth.make_inputs("llama3_8b_128k", seed=2, heads_limit=1)
+    assert q.shape[2] == 131072 and orc.default_chunk_size(131072) == 2048
+    _check_workload(q[:, :2].contiguous(), k, v, w.stride, w.threshold, 2048, True,
+                    sample_rows=[0, 1, 15, 16, 17, 100, 511, 512, 513, 800, 1022, 1023])
+
+
+def test_video_62k_full_length_two_query_heads():
+    """The qwen2vl_video_62k workload at its real length (62208 tokens, keys padded to 65536, default chunk
+    4096, S=16) on two query heads of one kv group: masks over all rows, outputs on 12 query blocks."""
+    from xattn_b200 import synth
+    q, k, v, w = synth.make_inputs("qwen2vl_video_62k", seed=3, heads_limit=1)
+    assert q.shape[2] == 62208 and orc.default_chunk_size(62208) == 4096
+    _check_workload(q[:, :2].contiguous(), k, v, w.stride, w.threshold, 4096, True,
+                    sample_rows=[0, 3, 4, 31, 32, 33, 200, 243, 300, 400, 484, 485])
+
+
+def test_dit_119k_full_length_two_heads():
+    """The hunyuan_dit_119k workload at its real length (119168 tokens, non-causal, S=8, threshold 0.95,
+    default chunk 2048: keys zero-padded to 120832, and the padded keys take softmax mass as in the
+    reference) on two heads: masks over all rows, outputs on 12 query blocks."""
+    from xattn_b200 import synth
+    g = torch.Generator().manual_seed(4)
+    q, k, v = synth.dit_like(g, 2)
+    q, k, v = q.bfloat16(), k.bfloat16(), v.bfloat16()
+    assert q.shape[2] == 119168 and orc.default_chunk_size(119168) == 2048
+    _check_workload(q, k, v, 8, 0.95, 2048, False,
+                    sample_rows=[0, 1, 15, 16, 100, 300, 464, 465, 700, 900, 929, 930])
+
+
+def test_llama_mha_4k_fp32_end_to_end():
+    """The fp32 reference-sized case (32 MHA heads, 4096 tokens, S=16, chunk 2048) through Xattention_prefill
+    on fp32 inputs.  Masks: against the fp32 oracle over all heads and rows.  Outputs: the attention phase
+    computes fp32 inputs in bf16 (the reference's attention backend takes 16-bit inputs only), so they are
+    checked against the oracle's attention on the bf16-rounded q/k/v under the GPU's mask."""
+    import xattn_b200
+    from xattn_b200 import synth
+    q, k, v, w = synth.make_inputs("llama_mha_4k_fp32", seed=0)
+    assert q.dtype == torch.float32 and q.shape == (1, 32, 4096, 128)
+    L = 4096
+    dq, dk, dv = q.to(DEV), k.to(DEV), v.to(DEV)
+    sums, mask = xattn_b200.xattn_estimate(dq, dk, 128, w.stride, threshold=w.threshold, chunk_size=w.chunk_size)
+    osums, omask = orc.xattn_estimate_oracle(q, k, 128, w.stride, 1.0, w.threshold, w.chunk_size, True)
+    assert sums.dtype == torch.float32
+    assert torch.allclose(sums.cpu(), osums, rtol=SUMS_RTOL, atol=SUMS_ATOL), (sums.cpu() - osums).abs().max()
+    ex = orc.margin_exempt(osums, L, L, 128, w.stride, w.chunk_size, w.threshold, True)
+    d = (mask.cpu() != omask) & ~ex
+    assert not d.any(), d.nonzero()[:6].tolist()
+    out = xattn_b200.Xattention_prefill(dq, dk, dv, w.stride, threshold=w.threshold, chunk_size=w.chunk_size)
+    assert out.dtype == torch.float32 and out.shape == q.shape
+    qr, kr, vr = q.bfloat16(), k.bfloat16(), v.bfloat16()
+    errs = []
+    for r in (0, 5, 15, 16, 17, 31):
+        r0, r1 = r * 128, (r + 1) * 128
+        ref = orc.block_sparse_attention_oracle(qr[:, :, r0:r1], kr[:, :, :r1], vr[:, :, :r1],
+                                                mask.cpu()[:, :, r:r + 1, : r + 1], True)
+        errs.append((out[:, :, r0:r1].cpu() - ref).abs())
+    err = torch.cat(errs, dim=2)
+    assert err.max() < OUT_MAX_ABS and err.mean() < OUT_MEAN_ABS, (err.max(), err.mean())
 
 
 def test_video_prefill_like_workload_padded_causal():
@@ -440,6 +521,13 @@ def test_query_chunk_shards_equal_the_full_call():
                                                 threshold=0.9, stride=16)
             for c, o in parts.items():
                 _assert_same_up_to_body_choice(o, full[:, :, c * 2048:(c + 1) * 2048], msg=str((world, r, c)))
+    # pieces of two estimate chunks each (fewer, larger launches per rank)
+    for r in range(2):
+        parts = prefill_query_chunk_sharded(dq, dk, dv, xattn_b200.Xattention_prefill, 2, r, 2048, threshold=0.9,
+                                            shard_rows=4096, stride=16)
+        assert sorted(parts) == [r]
+        for c, o in parts.items():
+            _assert_same_up_to_body_choice(o, full[:, :, c * 4096:(c + 1) * 4096], msg=str(("rows 4096", r, c)))
 
 
 def test_prefill_against_a_longer_key_cache():

@@ -7,7 +7,7 @@ import numpy as np
 import pytest
 import torch
 
-from make_golden import case_inputs, rope_inputs
+from make_golden import attention_inputs, case_inputs, rope_inputs
 from oracle import xattn_oracle as orc
 
 GOLD = os.path.join(os.path.dirname(__file__), "golden")
@@ -100,6 +100,24 @@ def test_attention_oracle_dense_equals_sdpa():
         ref = torch.nn.functional.scaled_dot_product_attention(
             q, k.repeat_interleave(2, 1), v.repeat_interleave(2, 1), is_causal=causal)
         assert torch.allclose(o, ref, atol=2e-5, rtol=1e-4)
+
+
+def test_attention_oracle_matches_the_reference_blockwise_attention():
+    """The attention oracle against outputs of the reference's own statement of causal block-sparse attention
+    (xattn/src/Flexprefill.py:12-44, torch_block_wise_attention), fp32 on both sides."""
+    z, specs = _load("attention_blockwise.npz")
+    assert len(specs) >= 4
+    for i, spec in enumerate(specs):
+        q, k, v, m = attention_inputs(spec)
+        chk = float(q.double().sum() + 3.0 * k.double().sum() + 5.0 * v.double().sum())
+        assert abs(chk - spec["checksum"]) <= 1e-6 * max(1.0, abs(chk)), "input generator drifted"
+        shape = spec["mask_shape"]
+        ref_m = np.unpackbits(z[f"mask_{i}"])[: int(np.prod(shape))].reshape(shape).astype(bool)
+        assert np.array_equal(m.numpy(), ref_m)
+        o = orc.block_sparse_attention_oracle(q, k, v, m, causal=True)
+        ref = torch.from_numpy(z[f"out_{i}"])
+        assert (o[..., :: spec["col_step"]] - ref).abs().max() <= 1e-5, spec
+        assert (o.double().sum(-1) - torch.from_numpy(z[f"rowsum_{i}"])).abs().max() <= 1e-4, spec
 
 
 def test_rotary_embedding_oracle_matches_the_reference_function_bit_for_bit():

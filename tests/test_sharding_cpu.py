@@ -108,6 +108,26 @@ def _worker_qchunks(rank, world, port, ret):
     dist.destroy_process_group()
 
 
+def test_query_pieces_of_several_chunks_equal_the_full_call():
+    """Pieces larger than one estimate chunk (shard_rows = 2 chunks): each piece, computed against the keys up to
+    its own end, equals the rows of the single call (no process group needed: no broadcast is requested)."""
+    from xattn_b200.sharding import prefill_query_chunk_sharded
+    g = torch.Generator().manual_seed(55)
+    L, chunk = 1024, 256
+    q, k, v = (torch.randn(1, 2, L, 128, generator=g) for _ in range(3))
+    want = _oracle_prefill(q, k, v, 0.9, 16, chunk, True)
+    seen = []
+    for rank in range(2):
+        parts = prefill_query_chunk_sharded(q, k, v, _oracle_prefill, 2, rank, chunk, threshold=0.9,
+                                            shard_rows=512, stride=16)
+        for c, o in parts.items():
+            seen.append(c)
+            assert float((o - want[:, :, c * 512:(c + 1) * 512]).abs().max()) < 1e-5
+    assert sorted(seen) == [0, 1]
+    with pytest.raises(ValueError):
+        prefill_query_chunk_sharded(q, k, v, _oracle_prefill, 2, 0, chunk, shard_rows=384, stride=16)
+
+
 def test_query_chunk_sharding_with_kv_broadcast_gloo():
     port = 31500 + (os.getpid() % 2000)
     mgr = mp.Manager()

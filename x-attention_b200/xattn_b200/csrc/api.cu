@@ -27,7 +27,9 @@ int block_sparse_attn_launch(const void* q, const void* k, const void* v, int dt
 
 extern "C" {
 
-int xattn_b200_version(void) { return 100; }
+int xattn_b200_version(void) { return 101; }
+
+unsigned long long xattn_b200_launch_count(void) { return xb::launch_counter().load(std::memory_order_relaxed); }
 
 const char* xattn_b200_error_string(int code) {
   switch (code) {

@@ -5,6 +5,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "../../../include/xattn_b200.h"
 
 namespace xb {
@@ -66,6 +68,16 @@ inline int sm_count() {
   return n > 0 ? n : 148;
 }
 
-inline int launch_status() { return cudaGetLastError() == cudaSuccess ? XATTN_B200_OK : XATTN_B200_ERR_CUDA; }
+// Kernel launches issued by this library in this process (every launcher calls launch_status() right after its
+// <<<>>>): a diagnostic the benchmark reads through xattn_b200_launch_count().
+inline std::atomic<unsigned long long>& launch_counter() {
+  static std::atomic<unsigned long long> n{0};
+  return n;
+}
+
+inline int launch_status() {
+  launch_counter().fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError() == cudaSuccess ? XATTN_B200_OK : XATTN_B200_ERR_CUDA;
+}
 
 }  // namespace xb

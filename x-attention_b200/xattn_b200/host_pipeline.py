@@ -167,4 +167,5 @@ def Xattention_prefill_host(query_states: torch.Tensor, key_states: torch.Tensor
         compute.wait_stream(d2h)
         compute.wait_stream(h2d)
         compute.synchronize()
+        ops.check_device_status(dev, synchronize=False)      # a kernel whose bounded wait ran out: raise, not garbage
     return out

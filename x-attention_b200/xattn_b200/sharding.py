@@ -95,26 +95,31 @@ def shard_query_chunks(n_chunks: int, world_size: int, rank: int) -> List[int]:
 
 def prefill_query_chunk_sharded(query_states: torch.Tensor, key_states: torch.Tensor, value_states: torch.Tensor,
                                 prefill_fn: Callable[..., torch.Tensor], world_size: int, rank: int, chunk_size: int,
-                                threshold=0.8, broadcast_kv_from: Optional[int] = None, group=None, **kwargs):
-    """Causal prefill with the QUERY axis cut into estimate chunks that are dealt to the ranks; every rank
-    needs all of K and V (one collective: `broadcast_kv_from` = source rank broadcasts them, NCCL over NVLink
-    on GPUs), kernels then read local memory only.
+                                threshold=0.8, broadcast_kv_from: Optional[int] = None, group=None,
+                                shard_rows: Optional[int] = None, **kwargs):
+    """Causal prefill with the QUERY axis cut into pieces that are dealt to the ranks; every rank needs all of
+    K and V (one collective: `broadcast_kv_from` = source rank broadcasts them, NCCL over NVLink on GPUs),
+    kernels then read local memory only.
 
-    A causal row never looks past its own chunk, so chunk c is computed exactly by the unchanged single-GPU
-    call on q[chunk c] against k/v[: end of chunk c] (queries aligned to the end of the keys, which is the
-    layout the path already supports for prefill against a cache): same block offsets, same first-chunk rule,
-    same normalisation as in the one-GPU run.  Returns {chunk index: output [B,Hq,rows,D]} for the local chunks.
-    q_len must equal k_len and be a multiple of chunk_size."""
+    A piece is `shard_rows` query rows (a multiple of the estimate's `chunk_size`; default: one chunk).  Piece c
+    is computed exactly by the unchanged single-GPU call on q[piece c] against k/v[: end of piece c] (queries
+    aligned to the end of the keys, which is the layout the path already supports for prefill against a cache):
+    same block offsets, same first-chunk rule, same normalisation as in the one-GPU run.  Larger pieces mean
+    fewer, larger launches per rank.  Returns {piece index: output [B,Hq,rows,D]} for the local pieces.
+    q_len must equal k_len and be a multiple of shard_rows."""
     if broadcast_kv_from is not None:
         import torch.distributed as dist
         dist.broadcast(key_states, src=broadcast_kv_from, group=group)
         dist.broadcast(value_states, src=broadcast_kv_from, group=group)
+    rows = chunk_size if shard_rows is None else int(shard_rows)
     L = query_states.shape[2]
-    if key_states.shape[2] != L or L % chunk_size != 0:
-        raise ValueError("query-chunk sharding needs q_len == k_len, a multiple of chunk_size")
+    if rows % chunk_size != 0:
+        raise ValueError("shard_rows must be a multiple of chunk_size")
+    if key_states.shape[2] != L or L % rows != 0:
+        raise ValueError("query-chunk sharding needs q_len == k_len, a multiple of the piece length")
     out = {}
-    for c in shard_query_chunks(L // chunk_size, world_size, rank):
-        r0, r1 = c * chunk_size, (c + 1) * chunk_size
+    for c in shard_query_chunks(L // rows, world_size, rank):
+        r0, r1 = c * rows, (c + 1) * rows
         out[c] = prefill_fn(query_states[:, :, r0:r1], key_states[:, :, :r1], value_states[:, :, :r1],
                             threshold=threshold, chunk_size=chunk_size, causal=True, **kwargs)
     return out

@@ -1,8 +1,10 @@
 """Seeded synthetic Q/K/V generators with the shapes and value structure of the workloads the
 reference is evaluated on (long-context Llama prefill, Qwen2-VL video prefill, HunyuanVideo
 DiT self-attention).  They stand in for real model activations, which are not available
-offline.  Everything is generated on the CPU in fp32 from a ``torch.Generator`` so that a
-seed fully determines the tensors.
+offline.  Everything is generated in fp32 from a ``torch.Generator`` so that a seed fully determines the
+tensors: on the CPU by default (what the tests and fixtures use), or directly on a CUDA device
+(``make_inputs(..., device=...)``; a different random stream, for benchmarks that need the long
+sequences quickly).
 
 Layout of every returned tensor: ``[1, H, L, D]`` contiguous.
 """
@@ -20,6 +22,7 @@ def _ar1(noise: torch.Tensor, rho: float, dim: int) -> torch.Tensor:
     x_t = rho x_{t-1} + sqrt(1-rho^2) e_t.  Computed blockwise in fp64 with the closed form
     x_{t0+u} = rho^u (x_{t0} + sum_{v<=u} rho^{-v} c e_{t0+v})."""
     x = noise.transpose(dim, -1).to(torch.float64)
+    dev = x.device
     T = x.shape[-1]
     c = math.sqrt(1.0 - rho * rho)
     out = torch.empty_like(x)
@@ -29,12 +32,12 @@ def _ar1(noise: torch.Tensor, rho: float, dim: int) -> torch.Tensor:
         e = x[..., t0:t0 + blk].clone()
         n = e.shape[-1]
         if prev is None:
-            u = torch.arange(n, dtype=torch.float64)
+            u = torch.arange(n, dtype=torch.float64, device=dev)
             e[..., 1:] *= c
             w = e * rho ** (-u)
             out[..., t0:t0 + n] = w.cumsum(-1) * rho ** u
         else:
-            u = torch.arange(1, n + 1, dtype=torch.float64)
+            u = torch.arange(1, n + 1, dtype=torch.float64, device=dev)
             w = (e * c) * rho ** (-u)
             out[..., t0:t0 + n] = (prev[..., None] + w.cumsum(-1)) * rho ** u
         prev = out[..., t0 + n - 1]
@@ -42,7 +45,7 @@ def _ar1(noise: torch.Tensor, rho: float, dim: int) -> torch.Tensor:
 
 
 def _unit(gen: torch.Generator, *shape) -> torch.Tensor:
-    u = torch.randn(*shape, generator=gen)
+    u = torch.randn(*shape, generator=gen, device=gen.device)
     return u / u.norm(dim=-1, keepdim=True)
 
 
@@ -71,13 +74,13 @@ def llama_like(gen: torch.Generator, hq: int, hkv: int, L: int, D: int = 128,
     v_t = N(0,I).  Returns q [1,hq,L,D], k, v [1,hkv,L,D]."""
     rep = hq // hkv
     u = _unit(gen, hkv, 1, D)
-    s = _ar1(torch.randn(hkv, L, D, generator=gen), rho, dim=1) * local_std
-    k = torch.randn(hkv, L, D, generator=gen) + s
+    s = _ar1(torch.randn(hkv, L, D, generator=gen, device=gen.device), rho, dim=1) * local_std
+    k = torch.randn(hkv, L, D, generator=gen, device=gen.device) + s
     k[:, :sink_tokens] += sink_dir * u
-    q = torch.randn(hq, L, D, generator=gen)
+    q = torch.randn(hq, L, D, generator=gen, device=gen.device)
     q += s.repeat_interleave(rep, dim=0)
     q += (q_dir * u).repeat_interleave(rep, dim=0)
-    v = torch.randn(hkv, L, D, generator=gen)
+    v = torch.randn(hkv, L, D, generator=gen, device=gen.device)
     return q[None], k[None], v[None]
 
 
@@ -91,16 +94,16 @@ def video_like(gen: torch.Generator, hq: int, hkv: int, text_pre: int = 512, fra
     rep = hq // hkv
     L = text_pre + frames * frame_tokens + text_post
     u = _unit(gen, hkv, 1, D)
-    f = _ar1(torch.randn(hkv, frames, D, generator=gen), rho, dim=1) * frame_std
-    k = torch.randn(hkv, L, D, generator=gen)
-    q = torch.randn(hq, L, D, generator=gen)
+    f = _ar1(torch.randn(hkv, frames, D, generator=gen, device=gen.device), rho, dim=1) * frame_std
+    k = torch.randn(hkv, L, D, generator=gen, device=gen.device)
+    q = torch.randn(hq, L, D, generator=gen, device=gen.device)
     fm = f.repeat_interleave(frame_tokens, dim=1)
     k[:, text_pre:text_pre + frames * frame_tokens] += fm
     q[:, text_pre:text_pre + frames * frame_tokens] += fm.repeat_interleave(rep, dim=0)
     k[:, :sink_tokens] += sink_dir * u
     q[:, :text_pre] += (q_dir * u).repeat_interleave(rep, dim=0)
     q[:, L - text_post:] += (q_dir * u).repeat_interleave(rep, dim=0)
-    v = torch.randn(hkv, L, D, generator=gen)
+    v = torch.randn(hkv, L, D, generator=gen, device=gen.device)
     return q[None], k[None], v[None]
 
 
@@ -113,18 +116,18 @@ def dit_like(gen: torch.Generator, heads: int, frames: int = 33, rows: int = 45,
     n_img = frames * rows * cols
     L = n_img + text_tokens
     L = (L + pad_to - 1) // pad_to * pad_to
-    field = torch.randn(heads, frames, rows, cols, D, generator=gen)
+    field = torch.randn(heads, frames, rows, cols, D, generator=gen, device=gen.device)
     for ax in (1, 2, 3):
         field = _ar1(field, rho, dim=ax)
     field = field.reshape(heads, n_img, D) * local_std
     u = _unit(gen, heads, 1, D)
-    q = torch.randn(heads, L, D, generator=gen)
-    k = torch.randn(heads, L, D, generator=gen)
+    q = torch.randn(heads, L, D, generator=gen, device=gen.device)
+    k = torch.randn(heads, L, D, generator=gen, device=gen.device)
     q[:, :n_img] += field
     k[:, :n_img] += field
     q[:, n_img:n_img + text_tokens] += text_dir * u
     k[:, n_img:n_img + text_tokens] += text_dir * u
-    v = torch.randn(heads, L, D, generator=gen)
+    v = torch.randn(heads, L, D, generator=gen, device=gen.device)
     return q[None], k[None], v[None]
 
 
@@ -143,11 +146,12 @@ WORKLOADS = {
 
 
 def make_inputs(name: str, seed: int = 0, heads_limit: Optional[int] = None,
-                seq_len: Optional[int] = None):
+                seq_len: Optional[int] = None, device=None):
     """Generate (q, k, v, workload) for a named workload.  ``heads_limit`` keeps only the first
-    kv heads (and their q heads); ``seq_len`` overrides the length (decoder workloads only)."""
+    kv heads (and their q heads); ``seq_len`` overrides the length (decoder workloads only);
+    ``device`` generates on that device (tensors stay there) instead of the CPU."""
     w = WORKLOADS[name]
-    gen = torch.Generator().manual_seed(seed)
+    gen = (torch.Generator() if device is None else torch.Generator(device=device)).manual_seed(seed)
     hq, hkv = w.hq, w.hkv
     if heads_limit is not None:
         rep = hq // hkv
