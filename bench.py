@@ -181,8 +181,12 @@ def _reference_estimate_fn():
         ref = make_ref.load()
 
         def run(q1, k1, w, chunk):
-            return ref.xattn_estimate(q1, k1, block_size=128, stride=w.stride, threshold=w.threshold,
-                                      chunk_size=chunk, use_triton=False, causal=w.causal)[1]
+            make_ref.keep_on_cpu(True)
+            try:
+                return ref.xattn_estimate(q1, k1, block_size=128, stride=w.stride, threshold=w.threshold,
+                                          chunk_size=chunk, use_triton=False, causal=w.causal)[1]
+            finally:
+                make_ref.keep_on_cpu(False)
         return run, "reference"
     from oracle import xattn_oracle as orc
 

@@ -18,8 +18,8 @@ does nothing and the benchmark falls back to the CPU restatement in ``oracle/xat
 its own environment (none of its files is changed):
   * a stub module ``block_sparse_attn`` (imported unconditionally at xattn/src/Xattention.py:10; the package
     is a third-party CUDA extension that is not part of the reference tree),
-  * on a machine without a GPU, ``Tensor.to("cuda")`` made a no-op (hard-coded at
-    xattn/src/Xattention.py:43,47,185,251).
+  * for the CPU arm (and always on a machine without a GPU), ``Tensor.to("cuda")`` of a CPU tensor made a
+    no-op (hard-coded at xattn/src/Xattention.py:43,47,185,251); see ``keep_on_cpu``.
 """
 from __future__ import annotations
 
@@ -56,6 +56,16 @@ def available() -> bool:
     return all(os.path.exists(os.path.join(REF_DIR, f)) for f in FILES)
 
 
+_keep_on_cpu = False
+
+
+def keep_on_cpu(flag: bool) -> None:
+    """While set, the reference's hard-coded ``.to("cuda")`` calls are no-ops, so CPU tensors stay on the CPU
+    (always the case on a machine without a GPU).  The CPU arm sets it; the GPU figures clear it."""
+    global _keep_on_cpu
+    _keep_on_cpu = bool(flag)
+
+
 def load():
     """Import the staged reference; returns the module ``xattn.src.Xattention`` of the staged copy."""
     if not available():
@@ -65,16 +75,20 @@ def load():
         stub = types.ModuleType("block_sparse_attn")
         stub.block_sparse_attn_func = None
         sys.modules["block_sparse_attn"] = stub
-    if not torch.cuda.is_available() and not getattr(torch.Tensor.to, "_xattn_ref_shim", False):
+    if not getattr(torch.Tensor.to, "_xattn_ref_shim", False):
         orig = torch.Tensor.to
 
         def _to(self, *a, **k):
-            if a and isinstance(a[0], str) and a[0].startswith("cuda"):
+            if (_keep_on_cpu or not torch.cuda.is_available()) and a and isinstance(a[0], str) \
+                    and a[0].startswith("cuda") and not self.is_cuda:
                 return self
             return orig(self, *a, **k)
 
         _to._xattn_ref_shim = True
         torch.Tensor.to = _to
+    if "xattn.src.Xattention" in sys.modules and \
+            os.path.abspath(getattr(sys.modules["xattn.src.Xattention"], "__file__", "")).startswith(REF_DIR):
+        return sys.modules["xattn.src.Xattention"]
     # the staged copy must win over the package's own `xattn` import-path shim
     for name in [n for n in sys.modules if n == "xattn" or n.startswith("xattn.")]:
         del sys.modules[name]

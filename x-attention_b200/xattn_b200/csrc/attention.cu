@@ -66,15 +66,16 @@ __device__ __forceinline__ uint32_t pack16(float lo, float hi, int is_bf16) {
 }
 
 // Development aid, compiled only with -DXB_TRACE: per-role timestamps of the first CTAs, written behind the
-// status word (which must then point to a device buffer of at least 64 + 16*7*2*XB_TRACE_CAP bytes).
+// status word (which must then point to a device buffer of at least 64 + 16*14*XB_TRACE_CAP bytes).  Roles: 0/5
+// loader, 1/6 MMA issuer of stream 0/1, 4 epilogue, softmax warp (stream s, quad q): q == 0 ? 2 + s : 7 + 3*s + q - 1.
 #ifdef XB_TRACE
 #ifndef XB_TRACE_CAP
-#define XB_TRACE_CAP 4096          // records per (CTA, role); 7 roles, first 2 CTAs
+#define XB_TRACE_CAP 4096          // records per role; 14 roles, first CTA only
 #endif
 __device__ __forceinline__ void xb_trace(int* status, uint32_t& n, int role, uint32_t tag, uint32_t val) {
-  if (blockIdx.x >= 2 || !status || n >= XB_TRACE_CAP) return;
+  if (blockIdx.x >= 1 || !status || n >= XB_TRACE_CAP) return;
   unsigned long long* buf = reinterpret_cast<unsigned long long*>(status) + 8 +
-                            2ull * XB_TRACE_CAP * (blockIdx.x * 7 + role);
+                            2ull * XB_TRACE_CAP * role;
   buf[2 * n] = (static_cast<unsigned long long>(tag) << 32) | val;
   buf[2 * n + 1] = static_cast<unsigned long long>(clock64());
   ++n;
@@ -143,7 +144,7 @@ __device__ __forceinline__ void attn_cta(const CUtensorMap& tmQ, const CUtensorM
                                          const CUtensorMap& tmKf, const CUtensorMap& tmVf, const AttnParams& p,
                                          const int32_t* __restrict__ block_idx, void* __restrict__ out, int* status) {
   // Shared memory takes nearly the whole L1, so a register spilled to local memory costs an L2 round trip:
-  // the split below is the one with which ptxas reports no spill for any role of this instantiation.
+  // the split below is the one with the fewest spills ptxas reports for this kernel (48 bytes, in cold paths).
 #ifdef XB_A_SM
   constexpr int kRegSoftmax = XB_A_SM, kRegEpilogue = XB_A_EP, kRegLoadMma = XB_A_LM;
 #else
@@ -167,7 +168,8 @@ __device__ __forceinline__ void attn_cta(const CUtensorMap& tmQ, const CUtensorM
   const int lane = threadIdx.x & 31;
 #ifdef XB_TRACE
   uint32_t trace_n = 0;
-  const int trace_role = warp < 4 ? 2 : (warp < 8 ? 3 : (warp < 12 ? 4 : (warp == 12 ? 0 : (warp == 13 ? 1 : (warp == 14 ? 5 : 6)))));
+  const int trace_role = warp < 8 ? ((warp & 3) == 0 ? 2 + (warp >> 2) : 7 + 3 * (warp >> 2) + (warp & 3) - 1)
+                                  : (warp < 12 ? 4 : (warp == 12 ? 0 : (warp == 13 ? 1 : (warp == 14 ? 5 : 6))));
 #endif
 
   // schedule table, built by the kernel before it picked this instantiation
@@ -421,7 +423,7 @@ __device__ __forceinline__ void attn_cta(const CUtensorMap& tmQ, const CUtensorM
     int n = n_items > 0 ? sch.cnt[sch.seq[s][0]] : 0;
     int win = n_items > 0 ? list_window(p, block_idx, it.row, n, 0, lane) : 0;
     for (int m = 0; m < n_items && ok; ++m) {
-      if (threadIdx.x == (s << 7)) XB_TRACE_EV(0x36, m);
+      if (lane == 0) XB_TRACE_EV(0x36, m);
       // the stream's next item: fetch its first list window while this one is processed
       Item nit = it;
       int nn = 0, nwin = 0;
@@ -448,11 +450,11 @@ __device__ __forceinline__ void attn_cta(const CUtensorMap& tmQ, const CUtensorM
           const int limit = row_last - k0 - 64 * h;       // columns c <= limit of this half are visible
           const bool masked = __any_sync(0xffffffffu, limit < 63);
           const uint32_t ts = ts0 + h * 64;
-          if (threadIdx.x == (s << 7)) XB_TRACE_EV(0x30, bc * 2 + h);
+          if (lane == 0) XB_TRACE_EV(0x30, bc * 2 + h);
           // waits are made warp-uniform: the tensor-memory loads/stores below are warp-collective
           if (!__all_sync(0xffffffffu, mbar_wait(bar(s, S_FULL + h), bc & 1, abort_flag))) { ok = false; break; }
           tc_fence_after();
-          if (threadIdx.x == (s << 7)) XB_TRACE_EV(0x31, bc * 2 + h);
+          if (lane == 0) XB_TRACE_EV(0x31, bc * 2 + h);
           // ---- pass 1: row maximum over the 64 columns, 8 chains of 3-input max, both loads in flight
           float mx8[8];
 #pragma unroll
@@ -487,7 +489,7 @@ __device__ __forceinline__ void attn_cta(const CUtensorMap& tmQ, const CUtensorM
             if (!first) {
               // O may be touched once every P.V issued so far for this stream has completed (the half before
               // this one is the latest: its P.V cannot have been issued before this half's P is ready)
-              if (threadIdx.x == (s << 7)) XB_TRACE_EV(0x32, bc * 2 + h);
+              if (lane == 0) XB_TRACE_EV(0x32, bc * 2 + h);
               const uint32_t hq = bc * 2 + h;
               if (!__all_sync(0xffffffffu, mbar_wait(bar(s, PV_DONE), (hq - 1) & 1, abort_flag))) { ok = false; break; }
               tc_fence_after();
@@ -505,7 +507,7 @@ __device__ __forceinline__ void attn_cta(const CUtensorMap& tmQ, const CUtensorM
             if (need) m_used = m_new;
           }
           const float m_ref = m_used == -INFINITY ? 0.f : m_used;
-          if (threadIdx.x == (s << 7)) XB_TRACE_EV(0x35, bc * 2 + h);
+          if (lane == 0) XB_TRACE_EV(0x35, bc * 2 + h);
           // ---- pass 2: exp2 of the two 32-column chunks; P chunk c (16 packed columns) overwrites S columns that
           // were read already
           const unsigned long long nmref2 = pack_f32x2(-m_ref, -m_ref);
@@ -547,7 +549,7 @@ __device__ __forceinline__ void attn_cta(const CUtensorMap& tmQ, const CUtensorM
           tc_wait_st();
           tc_fence_before();
           mbar_arrive(bar(s, P_READY + h));
-          if (threadIdx.x == (s << 7)) XB_TRACE_EV(0x33, bc * 2 + h);
+          if (lane == 0) XB_TRACE_EV(0x33, bc * 2 + h);
         }
       }
       it = nit; n = nn; win = nwin;
@@ -568,7 +570,7 @@ __device__ __forceinline__ void attn_cta(const CUtensorMap& tmQ, const CUtensorM
     int n = n_items > 0 ? sch.cnt[sch.seq[s][0]] : 0;
     int win = n_items > 0 ? list_window(p, block_idx, it.row, n, 0, lane) : 0;
     for (int m = 0; m < n_items && ok; ++m) {
-      if (threadIdx.x == (s << 7)) XB_TRACE_EV(0x36, m);
+      if (lane == 0) XB_TRACE_EV(0x36, m);
       // the stream's next item: fetch its first list window while this one is processed
       Item nit = it;
       int nn = 0, nwin = 0;
@@ -584,21 +586,21 @@ __device__ __forceinline__ void attn_cta(const CUtensorMap& tmQ, const CUtensorM
       if (p.causal && q_pos + k_off < row_last) row_last = q_pos + k_off;
       float m_used = -INFINITY, l = 0.f;
       int w = win, w_next = list_window(p, block_idx, row, n, 32, lane);
-      if (threadIdx.x == (s << 7)) XB_TRACE_EV(0x37, m);
+      if (lane == 0) XB_TRACE_EV(0x37, m);
       for (int j = 0; j < n; ++j, ++bc) {
         if (j > 0 && (j & 31) == 0) {
           w = w_next;
           w_next = list_window(p, block_idx, row, n, j + 32, lane);
         }
         const int k0 = __shfl_sync(0xffffffffu, w, j & 31) * 128;
-        if (threadIdx.x == (s << 7)) XB_TRACE_EV(0x38, bc);
+        if (lane == 0) XB_TRACE_EV(0x38, bc);
         const int limit = row_last - k0;                // columns c <= limit are visible
         const bool masked = __any_sync(0xffffffffu, limit < 127);
-        if (threadIdx.x == (s << 7)) XB_TRACE_EV(0x30, bc);
+        if (lane == 0) XB_TRACE_EV(0x30, bc);
         // waits are made warp-uniform: the tensor-memory loads/stores below are warp-collective
         if (!__all_sync(0xffffffffu, mbar_wait(s_full, bc & 1, abort_flag))) { ok = false; break; }
         tc_fence_after();
-        if (threadIdx.x == (s << 7)) XB_TRACE_EV(0x31, bc);
+        if (lane == 0) XB_TRACE_EV(0x31, bc);
         // ---- pass 1: row maximum, 8 independent chains of 3-input max.  In a masked block (diagonal / tail)
         // each 32-column chunk is classified per warp: all visible, none visible, or mixed (per-element
         // select).  The chunk loops are kept rolled: the kernel is bound by instruction issue and a small
@@ -657,7 +659,7 @@ __device__ __forceinline__ void attn_cta(const CUtensorMap& tmQ, const CUtensorM
           if (j > 0) {
             // S of block j is complete, and the tensor pipe runs in order, so the P.V of block j-1 of this
             // stream has completed too: O may be touched
-            if (threadIdx.x == (s << 7)) XB_TRACE_EV(0x32, bc);
+            if (lane == 0) XB_TRACE_EV(0x32, bc);
 #pragma unroll
             for (int c4 = 0; c4 < 4; ++c4) {
               uint32_t v[32];
@@ -672,7 +674,7 @@ __device__ __forceinline__ void attn_cta(const CUtensorMap& tmQ, const CUtensorM
           if (need) m_used = m_new;
         }
         const float m_ref = m_used == -INFINITY ? 0.f : m_used;
-        if (threadIdx.x == (s << 7)) XB_TRACE_EV(0x35, bc);
+        if (lane == 0) XB_TRACE_EV(0x35, bc);
         // ---- pass 2: exp2 in 32-column chunks; P chunk c4 (16 packed columns) overwrites S columns that were
         // read already (packed column c/2 <= c)
         const unsigned long long scale2 = pack_f32x2(p.scale_log2, p.scale_log2);
@@ -765,7 +767,7 @@ __device__ __forceinline__ void attn_cta(const CUtensorMap& tmQ, const CUtensorM
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(bar(s, P_READY + 1));
-        if (threadIdx.x == (s << 7)) XB_TRACE_EV(0x33, bc);
+        if (lane == 0) XB_TRACE_EV(0x33, bc);
       }
       it = nit; n = nn; win = nwin;
     }
