@@ -220,6 +220,27 @@ int xattn_b200_block_sparse_attn(const void* q, const void* k, const void* v, in
                                  const int32_t* block_cnt, int causal, float scale, void* out, int64_t o_stride_b,
                                  int64_t o_stride_h, int64_t o_stride_l, int* status, void* cuda_stream);
 
+/*
+ * The same operation with scratch memory, which lets the library treat the lists that long-context prefill
+ * produces most -- one or two blocks (attention sink + diagonal), identical for all query heads of a kv head --
+ * in a kernel of their own: K/V tiles loaded once per kv head and query block and shared by its query heads
+ * (GQA head sharing), both Q.K^T products and both P.V products issued back to back, one softmax pass without
+ * online rescaling.  Which rows qualify is decided on the device (no synchronisation); all other rows run through
+ * the general kernel of xattn_b200_block_sparse_attn.  Same call-site contract (xattn/src/Xattention.py:377-391),
+ * same results up to the summation order.
+ * workspace: device memory of xattn_b200_block_sparse_attn_workspace_bytes() bytes, 16-byte aligned, contents
+ * irrelevant on entry; the call's kernels use it until they finish.  A size of 0 means the shape gains nothing
+ * (hq / hkv odd or 1) and the call equals xattn_b200_block_sparse_attn; NULL is then accepted.
+ */
+size_t xattn_b200_block_sparse_attn_workspace_bytes(int batch, int hq, int hkv, int q_len, int k_len);
+int xattn_b200_block_sparse_attn_ws(const void* q, const void* k, const void* v, int dtype, int batch, int hq, int hkv,
+                                    int q_len, int k_len, int head_dim, int64_t q_stride_b, int64_t q_stride_h,
+                                    int64_t q_stride_l, int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_l,
+                                    int64_t v_stride_b, int64_t v_stride_h, int64_t v_stride_l,
+                                    const int32_t* block_idx, const int32_t* block_cnt, int causal, float scale,
+                                    void* out, int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_l,
+                                    void* workspace, size_t workspace_bytes, int* status, void* cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -230,6 +230,39 @@ def test_block_sparse_attention_vs_reference_blockwise_fixture():
         assert rs.max() < 128 * OUT_MEAN_ABS, (spec, rs.max())
 
 
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("dtype,hq,hkv,lq,lk", [(torch.bfloat16, 8, 2, 2048, 2048), (torch.float16, 4, 1, 1000, 1000),
+                                                (torch.bfloat16, 2, 1, 640, 1664), (torch.bfloat16, 6, 1, 1300, 1300)])
+def test_short_shared_lists_take_the_pair_kernel(causal, dtype, hq, hkv, lq, lk):
+    """Rows whose kv group shares a list of one or two blocks (sink + diagonal) run through the kernel that loads
+    K/V once per group; rows with longer lists, or lists that differ between the heads of a group, stay in the
+    general kernel.  Both against the oracle, and against the general kernel alone."""
+    from xattn_b200 import ops
+    g = torch.Generator().manual_seed(lq + hq)
+    q = torch.randn(1, hq, lq, 128, generator=g).to(dtype)
+    k = torch.randn(1, hkv, lk, 128, generator=g).to(dtype)
+    v = torch.randn(1, hkv, lk, 128, generator=g).to(dtype)
+    qb, kb = (lq + 127) // 128, (lk + 127) // 128
+    off = kb - qb
+    mask = torch.zeros(1, hq, qb, kb, dtype=torch.bool)
+    for r in range(qb):
+        mask[:, :, r, 0] = True
+        mask[:, :, r, min(off + r, kb - 1)] = True
+    mask[0, 0, 3, 1] = True            # one head of a group lists a third block: the whole group item stays general
+    mask[0, hq - 1, 2, 0] = False      # a list that differs inside a group
+    if qb > 5:
+        mask[0, :, 5, :] = False
+        mask[0, :, 5, min(off + 5, kb - 1)] = True      # a one-block list shared by all heads
+    idx, cnt = ops.mask_to_lists(mask.to(DEV), lq, lk, causal)
+    out = ops.block_sparse_attention(q.to(DEV), k.to(DEV), v.to(DEV), idx, cnt, causal,
+                                     use_pair_kernel=True).float().cpu()
+    ref = orc.block_sparse_attention_oracle(q, k, v, mask, causal)
+    err = (out - ref).abs()
+    assert err.max() < OUT_MAX_ABS and err.mean() < OUT_MEAN_ABS, (err.max(), err.mean())
+    gen = ops.block_sparse_attention(q.to(DEV), k.to(DEV), v.to(DEV), idx, cnt, causal, use_pair_kernel=False)
+    _assert_same_up_to_body_choice(out, gen.float().cpu())
+
+
 @pytest.mark.parametrize("causal,density,hq,hkv,L", [(True, 1.0, 2, 1, 4096), (False, 0.5, 2, 2, 3072), (True, 0.3, 4, 2, 5000)])
 def test_long_lists_take_the_half_block_path(causal, density, hq, hkv, L):
     """Rows that list many blocks run through the half-block instantiation of the kernel (each 128-key block

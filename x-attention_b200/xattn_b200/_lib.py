@@ -37,6 +37,10 @@ SIGNATURES = {
     "xattn_b200_block_sparse_attn": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _i, _i,
                                           _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64,
                                           _p, _p, _i, _f, _p, _i64, _i64, _i64, _p, _p]),
+    "xattn_b200_block_sparse_attn_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
+    "xattn_b200_block_sparse_attn_ws": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _i, _i,
+                                             _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64,
+                                             _p, _p, _i, _f, _p, _i64, _i64, _i64, _p, _sz, _p, _p]),
 }
 
 _lib = None

@@ -14,7 +14,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libxattn_b200.so")
-SOURCES = ["api.cu", "estimate.cu", "estimate_noalloc.cu", "select.cu", "attention.cu", "rope.cu"]
+SOURCES = ["api.cu", "estimate.cu", "estimate_noalloc.cu", "select.cu", "attention.cu", "attention_pair.cu", "rope.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-shared", "-diag-suppress", "550"]
 

@@ -22,7 +22,9 @@ int block_sparse_attn_launch(const void* q, const void* k, const void* v, int dt
                              int q_len, int k_len, int head_dim, int64_t qsb, int64_t qsh, int64_t qsl, int64_t ksb,
                              int64_t ksh, int64_t ksl, int64_t vsb, int64_t vsh, int64_t vsl,
                              const int32_t* block_idx, const int32_t* block_cnt, int causal, float scale, void* out,
-                             int64_t osb, int64_t osh, int64_t osl, int* status, cudaStream_t stream);
+                             int64_t osb, int64_t osh, int64_t osl, void* workspace, size_t workspace_bytes,
+                             int* status, cudaStream_t stream);
+size_t block_sparse_attn_workspace_bytes(int batch, int hq, int hkv, int q_len, int k_len);
 }  // namespace xb
 
 extern "C" {
@@ -135,7 +137,25 @@ int xattn_b200_block_sparse_attn(const void* q, const void* k, const void* v, in
   return xb::block_sparse_attn_launch(q, k, v, dtype, batch, hq, hkv, q_len, k_len, head_dim, q_stride_b, q_stride_h,
                                       q_stride_l, k_stride_b, k_stride_h, k_stride_l, v_stride_b, v_stride_h,
                                       v_stride_l, block_idx, block_cnt, causal, scale, out, o_stride_b, o_stride_h,
-                                      o_stride_l, status, static_cast<cudaStream_t>(cuda_stream));
+                                      o_stride_l, nullptr, 0, status, static_cast<cudaStream_t>(cuda_stream));
+}
+
+size_t xattn_b200_block_sparse_attn_workspace_bytes(int batch, int hq, int hkv, int q_len, int k_len) {
+  return xb::block_sparse_attn_workspace_bytes(batch, hq, hkv, q_len, k_len);
+}
+
+int xattn_b200_block_sparse_attn_ws(const void* q, const void* k, const void* v, int dtype, int batch, int hq, int hkv,
+                                    int q_len, int k_len, int head_dim, int64_t q_stride_b, int64_t q_stride_h,
+                                    int64_t q_stride_l, int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_l,
+                                    int64_t v_stride_b, int64_t v_stride_h, int64_t v_stride_l,
+                                    const int32_t* block_idx, const int32_t* block_cnt, int causal, float scale,
+                                    void* out, int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_l,
+                                    void* workspace, size_t workspace_bytes, int* status, void* cuda_stream) {
+  return xb::block_sparse_attn_launch(q, k, v, dtype, batch, hq, hkv, q_len, k_len, head_dim, q_stride_b, q_stride_h,
+                                      q_stride_l, k_stride_b, k_stride_h, k_stride_l, v_stride_b, v_stride_h,
+                                      v_stride_l, block_idx, block_cnt, causal, scale, out, o_stride_b, o_stride_h,
+                                      o_stride_l, workspace, workspace_bytes, status,
+                                      static_cast<cudaStream_t>(cuda_stream));
 }
 
 }  // extern "C"

@@ -251,11 +251,14 @@ def mask_to_lists(mask: torch.Tensor, q_len: int, k_len: int, causal: bool):
 # ------------------------------------------------------------------------------ phase 3
 def block_sparse_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, block_idx: torch.Tensor,
                            block_cnt: torch.Tensor, causal: bool = True, scale: Optional[float] = None,
-                           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                           out: Optional[torch.Tensor] = None, use_pair_kernel: bool = False) -> torch.Tensor:
     """q [B,Hq,Lq,128], k/v [B,Hkv,Lk,128] (bf16/fp16; fp32 is computed in bf16) -> [B,Hq,Lq,128], returned
     as a transposed view of [B,Lq,Hq,128] storage, like the reference's output (Xattention.py:392-394).
     `out`, if given, is a [B,Hq,Lq,128] tensor of the compute dtype (any strides, unit stride on the last
-    dimension, 16-byte aligned rows) that receives the result instead."""
+    dimension, 16-byte aligned rows) that receives the result instead.  `use_pair_kernel=True` sends the rows
+    whose kv group shares a list of one or two blocks to the kernel that loads K/V once per group and treats both
+    blocks in one softmax pass (xattn_b200_block_sparse_attn_ws); measured on a B200 it is on a par with the
+    general kernel on sink + diagonal masks and slower when many rows list three blocks, so it is off by default."""
     _require_cuda(q, k, v, block_idx, block_cnt)
     lib = _lib.load()
     B, Hq, Lq, D = q.shape
@@ -278,10 +281,12 @@ def block_sparse_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, bl
     lqb, lkb = (Lq + 127) // 128, (Lk + 127) // 128
     if tuple(block_idx.shape) != (B, Hq, lqb, lkb) or tuple(block_cnt.shape) != (B, Hq, lqb):
         raise ValueError("block lists have the wrong shape")
-    _lib.check(lib.xattn_b200_block_sparse_attn(
+    ws_bytes = lib.xattn_b200_block_sparse_attn_workspace_bytes(B, Hq, Hkv, Lq, Lk) if use_pair_kernel else 0
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device) if ws_bytes else None
+    _lib.check(lib.xattn_b200_block_sparse_attn_ws(
         q.data_ptr(), k.data_ptr(), v.data_ptr(), _DT[q.dtype], B, Hq, Hkv, Lq, Lk, D,
         *_strides3(q), *_strides3(k), *_strides3(v), block_idx.contiguous().data_ptr(),
         block_cnt.contiguous().data_ptr(), int(causal), scale, out_view.data_ptr(),
-        out_view.stride(0), out_view.stride(1), out_view.stride(2), _status(q.device).data_ptr(), _stream(q)),
-        "block_sparse_attn")
+        out_view.stride(0), out_view.stride(1), out_view.stride(2), ws.data_ptr() if ws is not None else 0, ws_bytes,
+        _status(q.device).data_ptr(), _stream(q)), "block_sparse_attn")
     return out_view.to(in_dtype) if (in_dtype == torch.float32 and out is None) else out_view
