@@ -72,9 +72,15 @@ int xattn_b200_default_chunk_size(int k_len);
  */
 int xattn_b200_estimate_geometry(int q_len, int k_len, int chunk_size, int stride, int block_size, int out[8]);
 
-/* Scratch needed by xattn_b200_estimate (bytes).  Host function, no CUDA call. */
+/* Scratch needed by xattn_b200_estimate (bytes), enough for any mask and semantics.  0: unsupported geometry.
+ * Host function, no CUDA call. */
 size_t xattn_b200_estimate_workspace_bytes(int batch, int hq, int q_len, int k_len, int stride, int block_size,
                                            int chunk_size);
+/* The same for one call's `causal` and `semantics` arguments.  Much smaller when the torch branch blanks every
+ * column left of a row's chunk (causal, keys not padded, XATTN_B200_SEMANTICS_TORCH or _TORCH_BAND): a row then
+ * keeps partial sums for its own chunk only (131072 tokens, stride 16, 32 heads: 20 MiB instead of 1 GiB). */
+size_t xattn_b200_estimate_workspace_bytes_ex(int batch, int hq, int q_len, int k_len, int stride, int block_size,
+                                              int chunk_size, int causal, int semantics);
 
 /*
  * Phase 1 -- antidiagonal block-importance estimate.
@@ -110,7 +116,7 @@ int xattn_b200_estimate(const void* q, const void* k, int dtype, int batch, int 
  * allocates and frees nothing; the caller still provides q, k and attn_sums.
  *
  * Arguments and results are those of xattn_b200_estimate (minus workspace/workspace_bytes).
- * Returns XATTN_B200_ERR_LIMIT when xattn_b200_estimate_workspace_bytes(...) for the problem exceeds
+ * Returns XATTN_B200_ERR_LIMIT when xattn_b200_estimate_workspace_bytes_ex(...) for the call exceeds
  * XATTN_B200_STATIC_SCRATCH_BYTES -- use xattn_b200_estimate with your own workspace then.
  *
  * The first call on each device looks up the array's device address (the device must be current, as

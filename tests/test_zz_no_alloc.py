@@ -50,12 +50,12 @@ def test_static_scratch_estimate_refuses_oversized_problems():
     from xattn_b200 import _lib
     lib = _lib.load()
     dev = torch.device("cuda", 0)
-    # 32 heads x 128K tokens needs ~1 GiB of scratch: far beyond the built-in array, and refused before
-    # any pointer is touched
-    assert lib.xattn_b200_estimate_workspace_bytes(1, 32, 131072, 131072, 16, 128, 2048) > (32 << 20)
+    # 32 heads x 128K tokens, non-causal (every row keeps partial sums for all 1024 key blocks), needs ~1 GiB of
+    # scratch: far beyond the built-in array, and refused before any pointer is touched
+    assert lib.xattn_b200_estimate_workspace_bytes_ex(1, 32, 131072, 131072, 16, 128, 2048, 0, 0) > (32 << 20)
     dummy = torch.zeros(16, device=dev)
     rc = lib.xattn_b200_estimate_static(
         dummy.data_ptr(), dummy.data_ptr(), 0, 1, 32, 8, 131072, 131072, 128,
-        0, 131072 * 128, 128, 0, 131072 * 128, 128, 16, 128, 2048, 0.01, 1, 0,
+        0, 131072 * 128, 128, 0, 131072 * 128, 128, 16, 128, 2048, 0.01, 0, 0,
         dummy.data_ptr(), 0, torch.cuda.current_stream().cuda_stream)
     assert rc == 5 and b"maximum" in lib.xattn_b200_error_string(rc)

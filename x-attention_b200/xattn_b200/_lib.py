@@ -23,6 +23,7 @@ SIGNATURES = {
     "xattn_b200_default_chunk_size": (_i, [_i]),
     "xattn_b200_estimate_geometry": (_i, [_i, _i, _i, _i, _i, C.POINTER(_i)]),
     "xattn_b200_estimate_workspace_bytes": (_sz, [_i, _i, _i, _i, _i, _i, _i]),
+    "xattn_b200_estimate_workspace_bytes_ex": (_sz, [_i, _i, _i, _i, _i, _i, _i, _i, _i]),
     "xattn_b200_estimate": (_i, [_p, _p, _i, _i, _i, _i, _i, _i, _i, _i64, _i64, _i64, _i64, _i64, _i64,
                                  _i, _i, _i, _f, _i, _i, _p, _p, _sz, _p, _p]),
     "xattn_b200_estimate_static": (_i, [_p, _p, _i, _i, _i, _i, _i, _i, _i, _i64, _i64, _i64, _i64, _i64, _i64,

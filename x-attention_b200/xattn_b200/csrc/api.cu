@@ -2,7 +2,8 @@
 #include "host_common.cuh"
 
 namespace xb {
-size_t estimate_workspace_bytes(int batch, int hq, int q_len, int k_len, int stride, int block_size, int chunk_size);
+size_t estimate_workspace_bytes(int batch, int hq, int q_len, int k_len, int stride, int block_size, int chunk_size,
+                                int causal, int semantics);
 int estimate_launch(const void* q, const void* k, int dtype, int batch, int hq, int hkv, int q_len, int k_len,
                     int head_dim, int64_t qsb, int64_t qsh, int64_t qsl, int64_t ksb, int64_t ksh, int64_t ksl,
                     int stride, int block_size, int chunk_size, float scale, int causal, int semantics,
@@ -70,7 +71,13 @@ int xattn_b200_estimate_geometry(int q_len, int k_len, int chunk_size, int strid
 
 size_t xattn_b200_estimate_workspace_bytes(int batch, int hq, int q_len, int k_len, int stride, int block_size,
                                            int chunk_size) {
-  return xb::estimate_workspace_bytes(batch, hq, q_len, k_len, stride, block_size, chunk_size);
+  return xb::estimate_workspace_bytes(batch, hq, q_len, k_len, stride, block_size, chunk_size, -1, 0);
+}
+
+size_t xattn_b200_estimate_workspace_bytes_ex(int batch, int hq, int q_len, int k_len, int stride, int block_size,
+                                              int chunk_size, int causal, int semantics) {
+  if (causal < 0) return 0;
+  return xb::estimate_workspace_bytes(batch, hq, q_len, k_len, stride, block_size, chunk_size, causal ? 1 : 0, semantics);
 }
 
 int xattn_b200_estimate(const void* q, const void* k, int dtype, int batch, int hq, int hkv, int q_len, int k_len,

@@ -49,6 +49,11 @@ struct EstGeom {
   int tile_n;                  // columns per tile: 256, or 128 when no row sees more than 128 columns
   int band;                    // attn_sums holds only the chunk's own key blocks (left_blank only): row stride bpc
   int bpc;                     // key blocks per chunk
+  // scratch layout: a reshaped row keeps m_pitch (max, sum) pairs and p_pitch partial block sums.  Dense: one per
+  // column tile / key block of the whole row.  Compact (left_blank: a row only ever touches the tiles of its own
+  // chunk): the column tiles [tile_lo, tile_lo + m_pitch) of its row tile, i.e. key blocks from tile_lo * (tile_n /
+  // rbs) on -- 16 floats per row instead of 1024 at 128K tokens.
+  int compact, m_pitch, p_pitch;
   float scale_log2;
 };
 
@@ -65,30 +70,41 @@ __host__ __device__ inline void row_bounds(const EstGeom& g, int i, int& lo, int
   if (hi > g.cols_valid - 1) hi = g.cols_valid - 1;
 }
 
+// first column tile / first key block a row tile's scratch rows are indexed from
+__host__ __device__ inline int scratch_tile0(const EstGeom& g, int nlo) { return g.compact ? nlo : 0; }
+__host__ __device__ inline int scratch_block0(const EstGeom& g, int nlo) {
+  return g.compact ? nlo * (g.tile_n / g.rbs) : 0;
+}
+// column-tile range of row tile mt: first tile and count (the formula of est_setup_kernel, also used by the host
+// to size the compact scratch)
+__host__ __device__ inline void row_tile_range(const EstGeom& g, int mt, int& first, int& count) {
+  // lo(i) and hi(i) never decrease with i, so the tile's column range is [lo(first row), hi(last valid row)]
+  const int i0 = mt * 128;
+  int i1 = i0 + 128;
+  if (i1 > g.rows_total) i1 = g.rows_total;
+  if (i1 > g.rows_valid) i1 = g.rows_valid;
+  int lo_min = 0, hi_max = -1;
+  if (i1 > i0) {
+    int lo, hi;
+    row_bounds(g, i0, lo_min, hi);
+    row_bounds(g, i1 - 1, lo, hi_max);
+  }
+  if (hi_max < lo_min) {
+    first = 0;
+    count = 0;
+  } else {
+    first = lo_min / g.tile_n;
+    count = hi_max / g.tile_n - lo_min / g.tile_n + 1;
+  }
+}
+
 // tile_lo[mt], tile_prefix[mt] (exclusive prefix of tile counts, n_mtiles+1 entries)
 __global__ void est_setup_kernel(EstGeom g, int* __restrict__ tile_lo, int* __restrict__ tile_prefix,
                                  int* __restrict__ pair_lo, int* __restrict__ pair_prefix) {
   extern __shared__ int s_cnt[];                  // [n_mtiles] tile counts, then [n_mtiles] first tiles
   int* s_lo = s_cnt + g.n_mtiles;
   for (int mt = threadIdx.x; mt < g.n_mtiles; mt += blockDim.x) {
-    // lo(i) and hi(i) never decrease with i, so the tile's column range is [lo(first row), hi(last valid row)]
-    const int i0 = mt * kTileM;
-    int i1 = i0 + kTileM;
-    if (i1 > g.rows_total) i1 = g.rows_total;
-    if (i1 > g.rows_valid) i1 = g.rows_valid;
-    int lo_min = 0, hi_max = -1;
-    if (i1 > i0) {
-      int lo, hi;
-      row_bounds(g, i0, lo_min, hi);
-      row_bounds(g, i1 - 1, lo, hi_max);
-    }
-    if (hi_max < lo_min) {
-      s_lo[mt] = 0;
-      s_cnt[mt] = 0;
-    } else {
-      s_lo[mt] = lo_min / g.tile_n;
-      s_cnt[mt] = hi_max / g.tile_n - lo_min / g.tile_n + 1;
-    }
+    row_tile_range(g, mt, s_lo[mt], s_cnt[mt]);
     tile_lo[mt] = s_lo[mt];
   }
   __syncthreads();
@@ -352,8 +368,10 @@ est_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const uint32_t taddr = tmem_base + acc * kTileN + (static_cast<uint32_t>(quad * 32) << 16);
       const bool row_ok = i < g.rows_total;
       const size_t rrow = static_cast<size_t>(bh) * g.rows_total + (row_ok ? i : 0);
-      est_epilogue_row<RBS>(g, taddr, n_chunks, clo, chi, row_ok, partial + rrow * g.kb_total, nt * kGroups,
-                            mtile + rrow * g.n_ntiles + nt, [&]() {
+      const int nlo = __ldg(tile_lo + mt);
+      est_epilogue_row<RBS>(g, taddr, n_chunks, clo, chi, row_ok,
+                            partial + rrow * g.p_pitch - scratch_block0(g, nlo), nt * kGroups,
+                            mtile + rrow * g.m_pitch + nt - scratch_tile0(g, nlo), [&]() {
                               // all TMEM reads of this accumulator are done: hand it back to the MMA thread
                               tc_fence_before();
                               __syncwarp();
@@ -523,8 +541,11 @@ est_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       const uint32_t taddr = tmem_base + acc * kTileN + (static_cast<uint32_t>(quad * 32) << 16);
       const bool row_ok = i < g.rows_total;
       const size_t rrow = static_cast<size_t>(bh) * g.rows_total + (row_ok ? i : 0);
-      est_epilogue_row<RBS>(g, taddr, n_chunks, clo, chi, row_ok, partial + rrow * g.kb_total, nt * kGroups,
-                            mtile + rrow * g.n_ntiles + nt, [&]() {
+      // (compact scratch: both row tiles of a pair lie in one chunk and start at the pair's first column tile)
+      const int nlo = __ldg(pair_lo + pm);
+      est_epilogue_row<RBS>(g, taddr, n_chunks, clo, chi, row_ok,
+                            partial + rrow * g.p_pitch - scratch_block0(g, nlo), nt * kGroups,
+                            mtile + rrow * g.m_pitch + nt - scratch_tile0(g, nlo), [&]() {
                               // all TMEM reads of this accumulator are done: hand it back to the MMA thread of
                               // the even CTA
                               tc_fence_before();
@@ -565,7 +586,7 @@ est_rowstat_kernel(const EstGeom g, const int* __restrict__ tile_lo, const int* 
   const int mt = i / kTileM;
   const int nlo = tile_lo[mt];
   const int ncnt = tile_prefix[mt + 1] - tile_prefix[mt];
-  const float2* mrow = mtile + static_cast<size_t>(idx) * g.n_ntiles + nlo;
+  const float2* mrow = mtile + static_cast<size_t>(idx) * g.m_pitch + nlo - scratch_tile0(g, nlo);
   float m = -INFINITY, l = 0.f;
   if (i < g.rows_valid) {
     for (int t = 0; t < ncnt; ++t) m = fmaxf(m, mrow[t].x);
@@ -600,7 +621,7 @@ est_blocksum_kernel(const EstGeom g, const int* __restrict__ tile_lo, const int*
     if (row < g.rbs) {                                     // whole 8-lane groups take the branch together
       float2 ms = make_float2(-INFINITY, 0.f);
       if (row < rows_ && slot < ncnt_)
-        ms = mtile[(static_cast<size_t>(bh) * g.rows_total + i0 + row) * g.n_ntiles + nlo_ + slot];
+        ms = mtile[(static_cast<size_t>(bh) * g.rows_total + i0 + row) * g.m_pitch + nlo_ - scratch_tile0(g, nlo_) + slot];
       const unsigned grp = 0xffu << (threadIdx.x & 24);    // the eight lanes of this row
       float m = ms.x;
       m = fmaxf(m, __shfl_xor_sync(grp, m, 1));
@@ -634,9 +655,9 @@ est_blocksum_kernel(const EstGeom g, const int* __restrict__ tile_lo, const int*
 #pragma unroll 2
     for (int row = 0; row < rows; ++row) {
       const float2 st = FUSED ? s_stat[row] : rowstat[r0 + row];
-      const float mx = mtile[(r0 + row) * g.n_ntiles + t].x;
+      const float mx = mtile[(r0 + row) * g.m_pitch + t - scratch_tile0(g, nlo)].x;
       const float f = (st.y > 0.f && mx > -INFINITY) ? exp2f(mx - st.x) * st.y : 0.f;
-      const float* pp = partial + (r0 + row) * g.kb_total + kb;
+      const float* pp = partial + (r0 + row) * g.p_pitch + kb - scratch_block0(g, nlo);
       if (VEC == 4) {
         const float4 pv = *reinterpret_cast<const float4*>(pp);
         if (f != 0.f) { acc[0] += pv.x * f; acc[1 % VEC] += pv.y * f; acc[2 % VEC] += pv.z * f; acc[3 % VEC] += pv.w * f; }
@@ -711,6 +732,19 @@ static int fill_geometry(int batch, int hq, int hkv, int q_len, int k_len, int h
   g.tile_n = (g.left_blank && g.rcs <= 128) ? 128 : kTileN;
   g.n_ntiles = (g.cols_total + g.tile_n - 1) / g.tile_n;
   g.scale_log2 = scale * 1.4426950408889634f;
+  g.compact = g.left_blank;
+  g.m_pitch = g.n_ntiles;
+  g.p_pitch = g.kb_total;
+  if (g.compact) {
+    int max_cnt = 1;
+    for (int mt = 0; mt < g.n_mtiles; ++mt) {
+      int first, cnt;
+      row_tile_range(g, mt, first, cnt);
+      max_cnt = cnt > max_cnt ? cnt : max_cnt;
+    }
+    g.m_pitch = max_cnt;
+    g.p_pitch = max_cnt * (g.tile_n / g.rbs);
+  }
   return XATTN_B200_OK;
 }
 
@@ -724,17 +758,32 @@ static EstWorkspace workspace_layout(const EstGeom& g) {
   w.off_pair_prefix = o; o = up(o + sizeof(int) * ((g.n_mtiles + 1) / 2 + 1));
   const size_t rows = static_cast<size_t>(g.batch) * g.hq * g.rows_total;
   w.off_rowstat = o; o = up(o + sizeof(float2) * rows);
-  w.off_mtile = o; o = up(o + sizeof(float2) * rows * g.n_ntiles);
-  w.off_partial = o; o = up(o + sizeof(float) * rows * g.kb_total);
+  w.off_mtile = o; o = up(o + sizeof(float2) * rows * g.m_pitch);
+  w.off_partial = o; o = up(o + sizeof(float) * rows * g.p_pitch);
   w.total = o;
   return w;
 }
 
-size_t estimate_workspace_bytes(int batch, int hq, int q_len, int k_len, int stride, int block_size, int chunk_size) {
+// Scratch of one estimate call: exact for the given mask and semantics, or (causal < 0) enough for any.
+size_t estimate_workspace_bytes(int batch, int hq, int q_len, int k_len, int stride, int block_size, int chunk_size,
+                                int causal, int semantics) {
   EstGeom g;
   const int ql = (q_len + stride - 1) / stride * stride, kl = (k_len + stride - 1) / stride * stride;
-  if (fill_geometry(batch, hq, hq, ql, kl, 128, stride, block_size, chunk_size, 1.f, 1, 0, g) != XATTN_B200_OK) return 0;
-  return workspace_layout(g).total;
+  if (causal >= 0) {
+    if (fill_geometry(batch, hq, hq, ql, kl, 128, stride, block_size, chunk_size, 1.f, causal, semantics, g) !=
+        XATTN_B200_OK)
+      return 0;
+    return workspace_layout(g).total;
+  }
+  size_t need = 0;
+  for (int c = 0; c < 2; ++c) {
+    if (fill_geometry(batch, hq, hq, ql, kl, 128, stride, block_size, chunk_size, 1.f, c, c ? XATTN_B200_SEMANTICS_TRITON : 0, g) !=
+        XATTN_B200_OK)
+      return 0;
+    const size_t t = workspace_layout(g).total;
+    need = t > need ? t : need;
+  }
+  return need;
 }
 
 int estimate_launch(const void* q, const void* k, int dtype, int batch, int hq, int hkv, int q_len, int k_len,
@@ -754,7 +803,11 @@ int estimate_launch(const void* q, const void* k, int dtype, int batch, int hq, 
   const EstWorkspace w = workspace_layout(g);
   if (!workspace || workspace_bytes < w.total) return XATTN_B200_ERR_WORKSPACE;
   if ((rc = check_sm100())) return rc;
-  if (g.n_mtiles > 8192) return XATTN_B200_ERR_LIMIT;
+  // every stated maximum is checked before the first launch, so that a refusal leaves no work in flight
+  const long long total_rows = static_cast<long long>(batch) * hq * g.rows_total;
+  if (g.n_mtiles > 8192 || total_rows > 0x7fffffffLL || static_cast<long long>(batch) * hq > 65535 ||
+      g.qb_total > 65535)
+    return XATTN_B200_ERR_LIMIT;
 
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   int* tile_lo = reinterpret_cast<int*>(ws + w.off_tile_lo);
@@ -782,6 +835,10 @@ int estimate_launch(const void* q, const void* k, int dtype, int batch, int hq, 
     if ((rc = make_tmap_16bit(&tmK, k, 5, dims, str, box))) return rc;
   }
 
+  // up to 64 KiB of dynamic shared memory (8192 row tiles): above the 48 KiB a kernel gets without asking
+  if (cudaFuncSetAttribute(est_setup_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * sizeof(int) * 8192) !=
+      cudaSuccess)
+    return XATTN_B200_ERR_CUDA;
   est_setup_kernel<<<1, 256, 2 * sizeof(int) * g.n_mtiles, stream>>>(g, tile_lo, tile_prefix, pair_lo, pair_prefix);
   if ((rc = launch_status())) return rc;
 
@@ -854,18 +911,17 @@ int estimate_launch(const void* q, const void* k, int dtype, int batch, int hq, 
   if (rc) return rc;
   }
 
-  const long long total_rows = static_cast<long long>(batch) * hq * g.rows_total;
-  if (total_rows > 0x7fffffffLL || batch * hq > 65535 || g.qb_total > 65535) return XATTN_B200_ERR_LIMIT;
   // rows that span at most eight column tiles: their statistics are computed inside est_blocksum_kernel
-  int max_tiles_per_row = g.n_ntiles;
-  // (a chunk starts at a multiple of rcs columns, so it is tile-aligned when rcs is a multiple of the tile width)
-  if (g.left_blank) max_tiles_per_row = g.rcs % g.tile_n == 0 ? g.rcs / g.tile_n : g.rcs / g.tile_n + 2;
+  const int max_tiles_per_row = g.m_pitch;             // (dense scratch: every column tile of the row)
   const int out_cols = g.band ? g.bpc : g.kb_total;
   const bool vec4 = g.kb_total % 4 == 0 && out_cols % 4 == 0 && (reinterpret_cast<uintptr_t>(attn_sums) & 15) == 0;
   const int per_row = vec4 ? out_cols / 4 : out_cols;
   // (and a query block with enough key blocks to amortise the extra round trip: measured -11 us at 32K, where a
   // CTA sums 128 key blocks, and +10 us at 128K, where it sums 16)
-  const bool fused = max_tiles_per_row <= 8 && per_row >= 32;
+#ifndef XB_FUSE_MIN
+#define XB_FUSE_MIN 32
+#endif
+  const bool fused = max_tiles_per_row <= 8 && per_row >= XB_FUSE_MIN;
   if (!fused) {
     est_rowstat_kernel<<<static_cast<int>((total_rows + 255) / 256), 256, 0, stream>>>(
         g, tile_lo, tile_prefix, mtile, rowstat, static_cast<int>(total_rows));

@@ -15,7 +15,8 @@
 #include "host_common.cuh"
 
 namespace xb {
-size_t estimate_workspace_bytes(int batch, int hq, int q_len, int k_len, int stride, int block_size, int chunk_size);
+size_t estimate_workspace_bytes(int batch, int hq, int q_len, int k_len, int stride, int block_size, int chunk_size,
+                                int causal, int semantics);
 int estimate_launch(const void* q, const void* k, int dtype, int batch, int hq, int hkv, int q_len, int k_len,
                     int head_dim, int64_t qsb, int64_t qsh, int64_t qsl, int64_t ksb, int64_t ksh, int64_t ksl,
                     int stride, int block_size, int chunk_size, float scale, int causal, int semantics,
@@ -30,8 +31,10 @@ namespace {
 constexpr int kMaxDevices = 64;
 void* g_scratch_addr[kMaxDevices] = {};   // device address of g_static_scratch, per device ordinal
 
-// Look up (first call on this device) or return the device address of the scratch array.
-// The device whose address is wanted must be current.
+// Look up (first call on this device) or return the device address of the scratch array.  The device whose
+// address is wanted must be current.  Two threads making the first call at once both store the same value.
+// The address belongs to the device's primary context: an application that resets the device
+// (cudaDeviceReset) must not use this entry point again in the same process.
 int static_scratch_for_current_device(void** out) {
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess) return XATTN_B200_ERR_CUDA;
@@ -52,11 +55,14 @@ extern "C" int xattn_b200_estimate_static(const void* q, const void* k, int dtyp
                                           int64_t k_stride_h, int64_t k_stride_l, int stride, int block_size,
                                           int chunk_size, float scale, int causal, int semantics, float* attn_sums,
                                           int* status, void* cuda_stream) {
-  const size_t need = xb::estimate_workspace_bytes(batch, hq, q_len, k_len, stride, block_size, chunk_size);
+  const size_t need = xb::estimate_workspace_bytes(batch, hq, q_len, k_len, stride, block_size, chunk_size,
+                                                   causal ? 1 : 0, semantics);
   if (need == 0) return XATTN_B200_ERR_ARG;
   if (need > static_cast<size_t>(XATTN_B200_STATIC_SCRATCH_BYTES)) return XATTN_B200_ERR_LIMIT;
+  int rc = xb::check_sm100();                       // a foreign device is an architecture error, not a CUDA error
+  if (rc != XATTN_B200_OK) return rc;
   void* scratch = nullptr;
-  const int rc = static_scratch_for_current_device(&scratch);
+  rc = static_scratch_for_current_device(&scratch);
   if (rc != XATTN_B200_OK) return rc;
   // Nothing in the scratch has to start at zero: the tile tables, the per-tile maxima and the partial
   // sums are all written by this call's kernels before this call's kernels read them.

@@ -15,7 +15,11 @@
 
 namespace xb {
 
-constexpr long long kWaitCycleLimit = 3000000000LL;   // ~1.5 s at 2 GHz; normal waits are microseconds
+// ~1.5 s at 2 GHz; normal waits are microseconds.  (A test build shortens it to make a wait run out on purpose.)
+#ifndef XB_WAIT_CYCLE_LIMIT
+#define XB_WAIT_CYCLE_LIMIT 3000000000LL
+#endif
+constexpr long long kWaitCycleLimit = XB_WAIT_CYCLE_LIMIT;
 
 // status codes written to the caller's status word by device code
 enum DeviceStatus : int {

@@ -154,7 +154,8 @@ def estimate_block_sums(q: torch.Tensor, k: torch.Tensor, stride: int, block_siz
         if q.dtype not in _DT or k.dtype != q.dtype:
             raise TypeError("q/k must both be bf16, fp16 or fp32")
         q, k, D_eff, dt = _aligned16(q), _aligned16(k), D, _DT[q.dtype]
-    ws_bytes = lib.xattn_b200_estimate_workspace_bytes(B, Hq, Lq_s, Lk_s, stride, block_size, chunk_size)
+    ws_bytes = lib.xattn_b200_estimate_workspace_bytes_ex(B, Hq, Lq_s, Lk_s, stride, block_size, chunk_size,
+                                                          int(causal), sem)
     if ws_bytes == 0:
         raise ValueError("unsupported estimate geometry (stride must be 4/8/16/32, block_size 128, "
                          "chunk_size a multiple of 128)")
