@@ -93,7 +93,10 @@ size_t xattn_b200_estimate_workspace_bytes_ex(int batch, int hq, int q_len, int 
  * emits per-row, per-key-block partial sums (into `workspace`), which a second small kernel
  * normalises into `attn_sums`.
  *
- * q_len / k_len must be multiples of `stride` (callers zero-pad a ragged tail);  head_dim is the
+ * q_len / k_len need not be multiples of `stride`: the tokens a ragged last stride group lacks count as the
+ * zeros the reference pads with (xattn/src/Xattention.py:42-51); the library stages a zero-padded copy of the
+ * one 128-row tile of Q (128- or 256-row tile of K) that holds that group in `workspace` -- a few MB instead
+ * of a padded copy of the tensors (workspace sizes assume head_dim 128 for it).  head_dim is the
  * length of a row in elements, a multiple of 64 (it may exceed the model's head dimension when
  * rows carry split-precision terms, see xattn_b200_split_f32);  `scale` = 1/(sqrt(D)*stride*norm).
  * attn_sums: float32 [batch, hq, q_blocks_pad, k_blocks_pad] (fully written).
@@ -137,11 +140,12 @@ int xattn_b200_estimate_static(const void* q, const void* k, int dtype, int batc
  * Split fp32 rows into three bf16 terms (x = hi + mid + lo) laid out as rows of 6*head_dim so that
  * a bf16 GEMM over the widened rows reproduces the fp32 product to ~2^-24:
  *   role 0 (query side): [hi, hi, mid, hi, lo, mid]     role 1 (key side): [hi, mid, hi, lo, hi, mid]
- * x is [batch, heads, len, head_dim] fp32 with element strides; out is contiguous
- * [batch, heads, len, 6*head_dim] bf16.  No counterpart in the reference (its torch branch
- * multiplies fp32 directly, xattn/src/Xattention.py:183).
+ * x is [batch, heads, len_valid, head_dim] fp32 with element strides; out is contiguous
+ * [batch, heads, len, 6*head_dim] bf16 with len >= len_valid, the rows past len_valid zero (the reference's
+ * zero padding, xattn/src/Xattention.py:42-51).  No counterpart in the reference (its torch branch multiplies
+ * fp32 directly, xattn/src/Xattention.py:183).
  */
-int xattn_b200_split_f32(const float* x, int batch, int heads, int len, int head_dim, int64_t stride_b,
+int xattn_b200_split_f32(const float* x, int batch, int heads, int len, int len_valid, int head_dim, int64_t stride_b,
                          int64_t stride_h, int64_t stride_l, int role, void* out, void* cuda_stream);
 
 /*

@@ -117,10 +117,40 @@ def test_estimate_strided_layout_and_ragged_length():
     L = 1003
     q = torch.randn(1, L, 3, 128, generator=g).bfloat16().transpose(1, 2)
     k = torch.randn(1, L, 3, 128, generator=g).bfloat16().transpose(1, 2)
-    got = ops.estimate_block_sums(q.to(DEV).transpose(1, 2).contiguous().transpose(1, 2),
-                                  k.to(DEV).transpose(1, 2).contiguous().transpose(1, 2), 16, 128, 2048, 1.0, True).cpu()
+    dq = q.to(DEV).transpose(1, 2).contiguous().transpose(1, 2)
+    dk = k.to(DEV).transpose(1, 2).contiguous().transpose(1, 2)
+    got = ops.estimate_block_sums(dq, dk, 16, 128, 2048, 1.0, True).cpu()
     want = orc.estimate_block_sums(q.float(), k.float(), 128, 16, 1.0, 2048, True, "torch")
     assert torch.allclose(got, want, rtol=SUMS_RTOL, atol=SUMS_ATOL), (got - want).abs().max()
+    # other strides, non-causal, and a longer ragged sequence whose last tile is not the first one
+    for S, causal, sem in ((8, False, "torch"), (4, True, "triton")):
+        got = ops.estimate_block_sums(dq, dk, S, 128, 2048, 1.0, causal, semantics=sem).cpu()
+        want = orc.estimate_block_sums(q.float(), k.float(), 128, S, 1.0, 2048, causal, sem)
+        assert torch.allclose(got, want, rtol=SUMS_RTOL, atol=SUMS_ATOL), (S, causal, (got - want).abs().max())
+
+
+def test_ragged_lengths_are_not_padded_by_copying():
+    """A length that is no multiple of the stride costs a staging copy of one tile per head, not a padded copy of
+    q and k (HunyuanVideo's real calls have such lengths at 118K tokens)."""
+    from xattn_b200 import ops
+    g = torch.Generator().manual_seed(6)
+    Lq, Lk, H = 40003, 40011, 2
+    q = torch.randn(1, H, Lq, 128, generator=g).bfloat16()
+    k = torch.randn(1, H, Lk, 128, generator=g).bfloat16()
+    dq, dk = q.to(DEV), k.to(DEV)
+    torch.cuda.synchronize()
+    torch.cuda.reset_peak_memory_stats()
+    base = torch.cuda.memory_allocated()
+    got = ops.estimate_block_sums(dq, dk, 8, 128, 4096, 1.0, False)
+    torch.cuda.synchronize()
+    extra = torch.cuda.max_memory_allocated() - base
+    want = orc.estimate_block_sums(q.float(), k.float(), 128, 8, 1.0, 4096, False, "torch")
+    assert torch.allclose(got.cpu(), want, rtol=SUMS_RTOL, atol=SUMS_ATOL), (got.cpu() - want).abs().max()
+    # scratch for the partial sums is inherent (rows x key blocks); a padded copy of q and k would add 20 MB more
+    rows, kb = want.shape[2] * 16, want.shape[3]
+    scratch = H * rows * (kb * 4 + 8 * ((kb + 15) // 16) + 8) + got.numel() * 4
+    assert extra < scratch + 4 * 1024 * 1024, (extra, scratch)
+    assert extra < scratch + (dq.numel() + dk.numel()) * 2 // 2
 
 
 def test_select_vs_find_blocks_chunked_fixtures():
@@ -640,6 +670,32 @@ def test_dit_varlen_wrapper_ragged_lengths():
     refs = orc.block_sparse_attention_oracle(qc, kc, vc, gmask.cpu(), False)
     err = (sparse[:, :, :valid].float().cpu() - refs).abs()
     assert err.max() < OUT_MAX_ABS and err.mean() < OUT_MEAN_ABS, (err.max(), err.mean())
+
+
+def test_dit_varlen_wrapper_makes_no_copies_of_its_inputs():
+    """At a length where copies would show (30K tokens, 4 heads: q, k, v 31 MB each): the peak device memory of
+    the call stays below the result plus the estimate's own scratch; contiguous copies of the three segments and a
+    concatenation of the outputs would add four times the size of q."""
+    from xattn_b200.dit_shim import xattn_varlen_attention
+    g = torch.Generator(device=DEV).manual_seed(3)
+    total, valid, H = 30000 + 77, 30000 - 13, 4
+    q, k, v = (torch.randn(1, H, total, 128, generator=g, device=DEV).bfloat16() for _ in range(3))
+    q[:, :, :256] += 4.0                            # a few strong keys, so that the selection stays sparse
+    k[:, :, :256] += 4.0
+    cu = torch.tensor([0, valid, total], dtype=torch.int32)
+    torch.cuda.synchronize()
+    torch.cuda.reset_peak_memory_stats()
+    base = torch.cuda.memory_allocated()
+    out = xattn_varlen_attention(q, k, v, cu, cu, threshold=0.9, stride=8)
+    torch.cuda.synchronize()
+    qbytes = q.numel() * q.element_size()
+    extra = torch.cuda.max_memory_allocated() - base
+    # result (1x) + partial sums of the non-causal estimate (rows x key blocks, fp32: 4 heads x 4096 x 256 x 4 B =
+    # 16 MB) + block sums, lists and the staged ragged tiles (a few MB)
+    assert extra < qbytes + 16 * (1 << 20) + 12 * (1 << 20), (extra, qbytes)
+    assert out.shape == q.shape and torch.isfinite(out.float()).all()
+    ref = torch.nn.functional.scaled_dot_product_attention(q[:, :, valid:], k[:, :, valid:], v[:, :, valid:])
+    assert (out[:, :, valid:].float() - ref.float()).abs().max() < OUT_MAX_ABS
 
 
 def test_rotary_embedding_matches_reference_fixture_bit_for_bit():

@@ -28,7 +28,7 @@ SIGNATURES = {
                                  _i, _i, _i, _f, _i, _i, _p, _p, _sz, _p, _p]),
     "xattn_b200_estimate_static": (_i, [_p, _p, _i, _i, _i, _i, _i, _i, _i, _i64, _i64, _i64, _i64, _i64, _i64,
                                         _i, _i, _i, _f, _i, _i, _p, _p, _p]),
-    "xattn_b200_split_f32": (_i, [_p, _i, _i, _i, _i, _i64, _i64, _i64, _i, _p, _p]),
+    "xattn_b200_split_f32": (_i, [_p, _i, _i, _i, _i, _i, _i64, _i64, _i64, _i, _p, _p]),
     "xattn_b200_rope_qk": (_i, [_p, _p, _i, _i, _i, _i, _i, _i, _i64, _i64, _i64, _i64, _i64, _i64, _p, _p, _i64, _i64, _p]),
     "xattn_b200_select": (_i, [_p, _i, _i, _i, _i, _i, _i, _i, _i, _d, _p, _i, _i, _p, _p, _p,
                                _i, _i, _i, _i, _p, _p]),

@@ -8,8 +8,8 @@ int estimate_launch(const void* q, const void* k, int dtype, int batch, int hq, 
                     int head_dim, int64_t qsb, int64_t qsh, int64_t qsl, int64_t ksb, int64_t ksh, int64_t ksl,
                     int stride, int block_size, int chunk_size, float scale, int causal, int semantics,
                     float* attn_sums, void* workspace, size_t workspace_bytes, int* status, cudaStream_t stream);
-int split_f32_launch(const float* x, int batch, int heads, int len, int head_dim, int64_t sb, int64_t sh, int64_t sl,
-                     int role, void* out, cudaStream_t stream);
+int split_f32_launch(const float* x, int batch, int heads, int len, int len_valid, int head_dim, int64_t sb, int64_t sh,
+                     int64_t sl, int role, void* out, cudaStream_t stream);
 int rope_qk_launch(void* q, void* k, int dtype, int batch, int hq, int hkv, int len, int head_dim, int64_t qsb,
                    int64_t qsh, int64_t qsl, int64_t ksb, int64_t ksh, int64_t ksl, const void* cos, const void* sin,
                    int64_t cs_stride_b, int64_t cs_stride_l, cudaStream_t stream);
@@ -91,9 +91,9 @@ int xattn_b200_estimate(const void* q, const void* k, int dtype, int batch, int 
                              static_cast<cudaStream_t>(cuda_stream));
 }
 
-int xattn_b200_split_f32(const float* x, int batch, int heads, int len, int head_dim, int64_t stride_b,
+int xattn_b200_split_f32(const float* x, int batch, int heads, int len, int len_valid, int head_dim, int64_t stride_b,
                          int64_t stride_h, int64_t stride_l, int role, void* out, void* cuda_stream) {
-  return xb::split_f32_launch(x, batch, heads, len, head_dim, stride_b, stride_h, stride_l, role, out,
+  return xb::split_f32_launch(x, batch, heads, len, len_valid, head_dim, stride_b, stride_h, stride_l, role, out,
                               static_cast<cudaStream_t>(cuda_stream));
 }
 

@@ -54,6 +54,10 @@ struct EstGeom {
   // chunk): the column tiles [tile_lo, tile_lo + m_pitch) of its row tile, i.e. key blocks from tile_lo * (tile_n /
   // rbs) on -- 16 floats per row instead of 1024 at 128K tokens.
   int compact, m_pitch, p_pitch;
+  // lengths that are no multiple of the stride: the row tile of Q' / column tile of K' that holds the ragged last
+  // stride group is read from a zero-padded staging copy of just that tile (-1: none)
+  int q_tail_mt, k_tail_nt;
+  int head_dim;
   float scale_log2;
 };
 
@@ -244,7 +248,8 @@ __device__ __forceinline__ void est_epilogue_row(const EstGeom& g, uint32_t tadd
 
 template <int RBS>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-est_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const EstGeom g,
+est_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmQt, const __grid_constant__ CUtensorMap tmKt, const EstGeom g,
                 const int* __restrict__ tile_lo, const int* __restrict__ tile_prefix, float* __restrict__ partial,
                 float2* __restrict__ mtile, const uint32_t idesc, int* status) {
   extern __shared__ uint8_t smem_raw[];
@@ -309,8 +314,11 @@ est_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           const int dc = ks - t * g.d_chunks;
           const uint32_t dstA = smem_u32(smem + s * stage_bytes);
           mbar_expect_tx(full0 + 8 * s, stage_bytes);
-          tma_load_5d(dstA, &tmQ, full0 + 8 * s, dc * kTileK, g.S - 1 - t, mt * kTileM, h, b);
-          tma_load_5d(dstA + kABytes, &tmK, full0 + 8 * s, dc * kTileK, t, nt * g.tile_n, h / group, b);
+          // (the tile that holds a ragged last stride group comes from its zero-padded staging copy)
+          const bool qt = mt == g.q_tail_mt, kt = nt == g.k_tail_nt;
+          tma_load_5d(dstA, qt ? &tmQt : &tmQ, full0 + 8 * s, dc * kTileK, g.S - 1 - t, qt ? 0 : mt * kTileM, h, b);
+          tma_load_5d(dstA + kABytes, kt ? &tmKt : &tmK, full0 + 8 * s, dc * kTileK, t, kt ? 0 : nt * g.tile_n,
+                      h / group, b);
         }
       }
     }
@@ -414,6 +422,7 @@ constexpr int kPairSmem = kPairStages * kPairStageBytes + 1024 /*barriers*/ + 10
 template <int RBS>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 est_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmKh,
+                     const __grid_constant__ CUtensorMap tmQt, const __grid_constant__ CUtensorMap tmKt,
                      const EstGeom g, const int* __restrict__ pair_lo, const int* __restrict__ pair_prefix,
                      float* __restrict__ partial, float2* __restrict__ mtile, const uint32_t idesc, int* status) {
   extern __shared__ uint8_t smem_raw[];
@@ -481,9 +490,10 @@ est_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           // all four loads of a stage are counted on the even CTA's barrier
           const uint32_t full_even = mapa_shared(full0 + 8 * s, 0);
           if (rank == 0) mbar_expect_tx(full0 + 8 * s, 2 * kPairStageBytes);
-          tma_load_5d_pair(dstA, &tmQ, full_even, dc * kTileK, g.S - 1 - t, mt * kTileM, h, b);
-          tma_load_5d_pair(dstA + kABytes, &tmKh, full_even, dc * kTileK, t, nt * kTileN + static_cast<int>(rank) * 128,
-                           h / group, b);
+          const bool qt = mt == g.q_tail_mt, kt = nt == g.k_tail_nt;
+          tma_load_5d_pair(dstA, qt ? &tmQt : &tmQ, full_even, dc * kTileK, g.S - 1 - t, qt ? 0 : mt * kTileM, h, b);
+          tma_load_5d_pair(dstA + kABytes, kt ? &tmKt : &tmKh, full_even, dc * kTileK, t,
+                           (kt ? 0 : nt * kTileN) + static_cast<int>(rank) * 128, h / group, b);
         }
       }
     }
@@ -672,8 +682,9 @@ est_blocksum_kernel(const EstGeom g, const int* __restrict__ tile_lo, const int*
 }
 
 // x = hi + mid + lo in bf16; rows widened to 6*D (see the header).
-__global__ void split_f32_kernel(const float* __restrict__ x, int heads, int len, int D, int64_t sb, int64_t sh,
-                                 int64_t sl, int role, __nv_bfloat16* __restrict__ out, size_t total) {
+// Rows l >= len_valid are written as zeros (a length rounded up to the stride).
+__global__ void split_f32_kernel(const float* __restrict__ x, int heads, int len, int len_valid, int D, int64_t sb,
+                                 int64_t sh, int64_t sl, int role, __nv_bfloat16* __restrict__ out, size_t total) {
   for (size_t e = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; e < total;
        e += static_cast<size_t>(gridDim.x) * blockDim.x) {
     const int d = static_cast<int>(e % D);
@@ -682,7 +693,7 @@ __global__ void split_f32_kernel(const float* __restrict__ x, int heads, int len
     rest /= len;
     const int h = static_cast<int>(rest % heads);
     const int b = static_cast<int>(rest / heads);
-    const float v = x[b * sb + h * sh + l * sl + d];
+    const float v = l < len_valid ? x[b * sb + h * sh + l * sl + d] : 0.f;
     const __nv_bfloat16 hi = __float2bfloat16_rn(v);
     const float r1 = v - __bfloat162float(hi);
     const __nv_bfloat16 mid = __float2bfloat16_rn(r1);
@@ -696,9 +707,31 @@ __global__ void split_f32_kernel(const float* __restrict__ x, int heads, int len
   }
 }
 
+// Zero-padded copy of `n_tokens` tokens starting at `first_token` of every head ([batch, heads, n_tokens, D] 16-bit,
+// contiguous): the tile that holds the ragged last stride group, so that the tokens past the end read as the zeros
+// the reference pads with (xattn/src/Xattention.py:42-51) instead of the next head's data.  16 bytes per thread.
+__global__ void est_tail_kernel(const uint4* __restrict__ src, int64_t sb, int64_t sh, int64_t sl, int heads, int len,
+                                int D, int first_token, int n_tokens, uint4* __restrict__ dst, size_t total_vec) {
+  const int vec_per_row = D / 8;
+  for (size_t e = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; e < total_vec;
+       e += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const int c = static_cast<int>(e % vec_per_row);
+    size_t rest = e / vec_per_row;
+    const int tok = static_cast<int>(rest % n_tokens);
+    rest /= n_tokens;
+    const int h = static_cast<int>(rest % heads);
+    const int b = static_cast<int>(rest / heads);
+    const int t = first_token + tok;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (t < len) v = src[(b * sb + h * sh + static_cast<int64_t>(t) * sl) / 8 + c];
+    dst[e] = v;
+  }
+}
+
 // ------------------------------------------------------------------------------------ host side
 struct EstWorkspace {
-  size_t off_tile_lo, off_tile_prefix, off_pair_lo, off_pair_prefix, off_rowstat, off_mtile, off_partial, total;
+  size_t off_tile_lo, off_tile_prefix, off_pair_lo, off_pair_prefix, off_rowstat, off_mtile, off_partial;
+  size_t off_qtail, off_ktail, total;
 };
 
 static int fill_geometry(int batch, int hq, int hkv, int q_len, int k_len, int head_dim, int stride, int block_size,
@@ -707,7 +740,6 @@ static int fill_geometry(int batch, int hq, int hkv, int q_len, int k_len, int h
   if (stride != 4 && stride != 8 && stride != 16 && stride != 32) return XATTN_B200_ERR_ARG;
   if (block_size != 128 || chunk_size < block_size || chunk_size % block_size != 0) return XATTN_B200_ERR_ARG;
   if (head_dim < kTileK || head_dim % kTileK != 0) return XATTN_B200_ERR_ARG;
-  if (q_len % stride != 0 || k_len % stride != 0) return XATTN_B200_ERR_ARG;
   const int k_pad = (chunk_size - k_len % chunk_size) % chunk_size;
   const int q_pad = (chunk_size - q_len % chunk_size) % chunk_size;
   const int lq = q_len + q_pad, lk = k_len + k_pad;
@@ -732,6 +764,9 @@ static int fill_geometry(int batch, int hq, int hkv, int q_len, int k_len, int h
   g.tile_n = (g.left_blank && g.rcs <= 128) ? 128 : kTileN;
   g.n_ntiles = (g.cols_total + g.tile_n - 1) / g.tile_n;
   g.scale_log2 = scale * 1.4426950408889634f;
+  g.head_dim = head_dim;
+  g.q_tail_mt = q_len % stride ? (q_len / stride) / kTileM : -1;
+  g.k_tail_nt = k_len % stride ? (k_len / stride) / g.tile_n : -1;
   g.compact = g.left_blank;
   g.m_pitch = g.n_ntiles;
   g.p_pitch = g.kb_total;
@@ -760,6 +795,11 @@ static EstWorkspace workspace_layout(const EstGeom& g) {
   w.off_rowstat = o; o = up(o + sizeof(float2) * rows);
   w.off_mtile = o; o = up(o + sizeof(float2) * rows * g.m_pitch);
   w.off_partial = o; o = up(o + sizeof(float) * rows * g.p_pitch);
+  // staging tiles [batch, heads, tile * S tokens, head_dim], 16 bit
+  w.off_qtail = o;
+  if (g.q_tail_mt >= 0) o = up(o + static_cast<size_t>(g.batch) * g.hq * kTileM * g.S * g.head_dim * 2);
+  w.off_ktail = o;
+  if (g.k_tail_nt >= 0) o = up(o + static_cast<size_t>(g.batch) * g.hkv * g.tile_n * g.S * g.head_dim * 2);
   w.total = o;
   return w;
 }
@@ -768,7 +808,7 @@ static EstWorkspace workspace_layout(const EstGeom& g) {
 size_t estimate_workspace_bytes(int batch, int hq, int q_len, int k_len, int stride, int block_size, int chunk_size,
                                 int causal, int semantics) {
   EstGeom g;
-  const int ql = (q_len + stride - 1) / stride * stride, kl = (k_len + stride - 1) / stride * stride;
+  const int ql = q_len, kl = k_len;      // (head_dim 128 and hkv = hq assumed for the staging tiles of ragged lengths)
   if (causal >= 0) {
     if (fill_geometry(batch, hq, hq, ql, kl, 128, stride, block_size, chunk_size, 1.f, causal, semantics, g) !=
         XATTN_B200_OK)
@@ -839,16 +879,45 @@ int estimate_launch(const void* q, const void* k, int dtype, int batch, int hq, 
   if (cudaFuncSetAttribute(est_setup_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * sizeof(int) * 8192) !=
       cudaSuccess)
     return XATTN_B200_ERR_CUDA;
-  est_setup_kernel<<<1, 256, 2 * sizeof(int) * g.n_mtiles, stream>>>(g, tile_lo, tile_prefix, pair_lo, pair_prefix);
-  if ((rc = launch_status())) return rc;
-
-  const int sms = sm_count();
   // CTA pairs (256x256 tiles) when tiles are 256 columns wide and the two row tiles of a pair see about the
   // same columns (always, except when a 128-row chunk of the torch branch blanks everything left of it)
   bool use_pairs = g.tile_n == kTileN && g.n_mtiles >= 2 && (!g.left_blank || g.rcs % (2 * kTileM) == 0);
 #ifdef XB_EST_NO_PAIRS
   use_pairs = false;
 #endif
+  // ragged lengths: stage the tile with the last (partial) stride group and map it like the tensor itself
+  CUtensorMap tmQt = tmQ, tmKt = tmK;
+  auto stage_tail = [&](const void* src, int64_t sb, int64_t sh, int64_t sl, int heads, int len, int tile_rows,
+                        int tail_tile, size_t off, uint32_t box_rows, CUtensorMap* map) -> int {
+    if ((sb % 8) || (sh % 8) || (sl % 8) || (head_dim % 8)) return XATTN_B200_ERR_ARG;
+    const int n_tokens = tile_rows * stride;
+    const size_t total_vec = static_cast<size_t>(batch) * heads * n_tokens * (head_dim / 8);
+    size_t blocks = (total_vec + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    est_tail_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(
+        static_cast<const uint4*>(src), sb, sh, sl, heads, len, head_dim, tail_tile * n_tokens, n_tokens,
+        reinterpret_cast<uint4*>(ws + off), total_vec);
+    int r = launch_status();
+    if (r) return r;
+    const uint64_t dims[5] = {(uint64_t)head_dim, (uint64_t)stride, (uint64_t)tile_rows, (uint64_t)heads,
+                              (uint64_t)batch};
+    const uint64_t tok = (uint64_t)head_dim * 2;
+    const uint64_t s_h = heads > 1 ? tok * n_tokens : 256, s_b = batch > 1 ? tok * n_tokens * heads : 256;
+    const uint64_t str[4] = {tok, tok * stride, s_h, s_b};
+    const uint32_t box[5] = {kTileK, 1, box_rows, 1, 1};
+    return make_tmap_16bit(map, ws + off, 5, dims, str, box);
+  };
+  if (g.q_tail_mt >= 0 &&
+      (rc = stage_tail(q, qsb, qsh, qsl, hq, q_len, kTileM, g.q_tail_mt, w.off_qtail, kTileM, &tmQt)))
+    return rc;
+  if (g.k_tail_nt >= 0 && (rc = stage_tail(k, ksb, ksh, ksl, hkv, k_len, g.tile_n, g.k_tail_nt, w.off_ktail,
+                                           use_pairs ? 128 : static_cast<uint32_t>(g.tile_n), &tmKt)))
+    return rc;
+
+  est_setup_kernel<<<1, 256, 2 * sizeof(int) * g.n_mtiles, stream>>>(g, tile_lo, tile_prefix, pair_lo, pair_prefix);
+  if ((rc = launch_status())) return rc;
+
+  const int sms = sm_count();
   if (use_pairs) {
     CUtensorMap tmKh;                     // K with a box of 128 rows: one CTA's half of a 256-column tile
     {
@@ -879,8 +948,8 @@ int estimate_launch(const void* q, const void* k, int dtype, int batch, int hq, 
       if (cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg) != cudaSuccess || max_clusters < 1)
         return XATTN_B200_ERR_CUDA;
       if (static_cast<unsigned>(2 * max_clusters) < cfg.gridDim.x) cfg.gridDim.x = 2 * max_clusters;
-      if (cudaLaunchKernelEx(&cfg, kern, tmQ, tmKh, g, (const int*)pair_lo, (const int*)pair_prefix, partial, mtile,
-                             idesc2, status) != cudaSuccess)
+      if (cudaLaunchKernelEx(&cfg, kern, tmQ, tmKh, tmQt, tmKt, g, (const int*)pair_lo, (const int*)pair_prefix,
+                             partial, mtile, idesc2, status) != cudaSuccess)
         return XATTN_B200_ERR_CUDA;
       return launch_status();
     };
@@ -898,7 +967,8 @@ int estimate_launch(const void* q, const void* k, int dtype, int batch, int hq, 
   auto launch = [&](auto kern) -> int {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem) != cudaSuccess)
       return XATTN_B200_ERR_CUDA;
-    kern<<<grid, kGemmThreads, kGemmSmem, stream>>>(tmQ, tmK, g, tile_lo, tile_prefix, partial, mtile, idesc, status);
+    kern<<<grid, kGemmThreads, kGemmSmem, stream>>>(tmQ, tmK, tmQt, tmKt, g, tile_lo, tile_prefix, partial, mtile, idesc,
+                                                    status);
     return launch_status();
   };
   switch (g.rbs) {
@@ -940,15 +1010,16 @@ int estimate_launch(const void* q, const void* k, int dtype, int batch, int hq, 
   return launch_status();
 }
 
-int split_f32_launch(const float* x, int batch, int heads, int len, int head_dim, int64_t sb, int64_t sh, int64_t sl,
-                     int role, void* out, cudaStream_t stream) {
-  if (!x || !out || batch < 1 || heads < 1 || len < 1 || head_dim < 1 || (role != 0 && role != 1))
+int split_f32_launch(const float* x, int batch, int heads, int len, int len_valid, int head_dim, int64_t sb, int64_t sh,
+                     int64_t sl, int role, void* out, cudaStream_t stream) {
+  if (!x || !out || batch < 1 || heads < 1 || len < 1 || len_valid < 1 || len_valid > len || head_dim < 1 ||
+      (role != 0 && role != 1))
     return XATTN_B200_ERR_ARG;
   const size_t total = static_cast<size_t>(batch) * heads * len * head_dim;
   const int block = 256;
   size_t blocks = (total + block - 1) / block;
   if (blocks > 148 * 32) blocks = 148 * 32;
-  split_f32_kernel<<<static_cast<int>(blocks), block, 0, stream>>>(x, heads, len, head_dim, sb, sh, sl, role,
+  split_f32_kernel<<<static_cast<int>(blocks), block, 0, stream>>>(x, heads, len, len_valid, head_dim, sb, sh, sl, role,
                                                                     static_cast<__nv_bfloat16*>(out), total);
   return launch_status();
 }

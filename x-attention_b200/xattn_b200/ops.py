@@ -90,16 +90,6 @@ def default_chunk_size(k_len: int) -> int:
     return _lib.load().xattn_b200_default_chunk_size(k_len)
 
 
-def _pad_to_stride(x: torch.Tensor, stride: int) -> torch.Tensor:
-    """Zero-pad the sequence to a multiple of `stride` (the reference zero-pads to a chunk multiple,
-    xattn/src/Xattention.py:42-51; whole missing groups are supplied by TMA zero fill, only a ragged
-    last group needs real zeros)."""
-    L = x.shape[2]
-    if L % stride == 0:
-        return x
-    return torch.nn.functional.pad(x, (0, 0, 0, stride - L % stride))
-
-
 def _aligned16(x: torch.Tensor) -> torch.Tensor:
     ok = x.stride(3) == 1 and x.data_ptr() % 16 == 0 and all((s * x.element_size()) % 16 == 0 for s in x.stride()[:3])
     return x if ok else x.contiguous()
@@ -134,26 +124,31 @@ def estimate_block_sums(q: torch.Tensor, k: torch.Tensor, stride: int, block_siz
             raise ValueError("band layout needs the torch branch, causal, and k_len a multiple of chunk_size")
         sem = _lib.SEMANTICS_TORCH_BAND
     scale = 1.0 / math.sqrt(D) / stride / norm
-    q = _pad_to_stride(q, stride)
-    k = _pad_to_stride(k, stride)
-    Lq_s, Lk_s = q.shape[2], k.shape[2]
+    # lengths that are no multiple of the stride go to the library as they are (it stages the one ragged tile);
+    # only the fp32 path rounds up, inside the split kernel that writes the widened rows anyway
+    Lq_s, Lk_s = Lq, Lk
     g = geometry(Lq, Lk, chunk_size, stride, block_size)
     stream = _stream(q)
     if q.dtype == torch.float32:
+        Lq_s, Lk_s = -(-Lq // stride) * stride, -(-Lk // stride) * stride
         q3 = torch.empty(B, Hq, Lq_s, 6 * D, dtype=torch.bfloat16, device=q.device)
         k3 = torch.empty(B, Hkv, Lk_s, 6 * D, dtype=torch.bfloat16, device=q.device)
         q = q if q.stride(3) == 1 else q.contiguous()
         k = k.float()
         k = k if k.stride(3) == 1 else k.contiguous()
-        _lib.check(lib.xattn_b200_split_f32(q.data_ptr(), B, Hq, Lq_s, D, *_strides3(q), 0, q3.data_ptr(), stream),
+        _lib.check(lib.xattn_b200_split_f32(q.data_ptr(), B, Hq, Lq_s, Lq, D, *_strides3(q), 0, q3.data_ptr(), stream),
                    "split_f32(q)")
-        _lib.check(lib.xattn_b200_split_f32(k.data_ptr(), B, Hkv, Lk_s, D, *_strides3(k), 1, k3.data_ptr(), stream),
+        _lib.check(lib.xattn_b200_split_f32(k.data_ptr(), B, Hkv, Lk_s, Lk, D, *_strides3(k), 1, k3.data_ptr(), stream),
                    "split_f32(k)")
         q, k, D_eff, dt = q3, k3, 6 * D, _lib.BF16
     else:
         if q.dtype not in _DT or k.dtype != q.dtype:
             raise TypeError("q/k must both be bf16, fp16 or fp32")
         q, k, D_eff, dt = _aligned16(q), _aligned16(k), D, _DT[q.dtype]
+        if D != 128 and (Lq % stride or Lk % stride):        # the staging tiles are sized for head_dim 128
+            pad = lambda x: torch.nn.functional.pad(x, (0, 0, 0, (-x.shape[2]) % stride))  # noqa: E731
+            q, k = pad(q), pad(k)
+            Lq_s, Lk_s = q.shape[2], k.shape[2]
     ws_bytes = lib.xattn_b200_estimate_workspace_bytes_ex(B, Hq, Lq_s, Lk_s, stride, block_size, chunk_size,
                                                           int(causal), sem)
     if ws_bytes == 0:
