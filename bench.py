@@ -42,9 +42,11 @@ import torch  # noqa: E402
 
 METRIC = "prefill_attention_effective_tflops"
 UNIT = "TFLOP/s (dense-equivalent, 4*Lq*Lk*D*Hq/2 causal)"
-# dram__bytes_read.sum + dram__bytes_write.sum of ONE block_sparse_attn_kernel launch on the full workload, from
-# ncu captures of this benchmark's own command line (None: not captured)
-NCU_ATTENTION_TRAFFIC_BYTES = {"llama3_8b_32k": None, "llama3_8b_128k": None}
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE block_sparse_attn_kernel launch, from ncu captures of this
+# benchmark's own command line.  32K: the full workload (405.4 MB read + 234.1 MB written).  128K: captured on two
+# of the eight kv-head groups (--heads-limit 2: 404.4 MB + 231.5 MB) and multiplied by four -- every (kv group)
+# reads and writes its own Q, K, V and O, so the traffic grows in proportion.
+NCU_ATTENTION_TRAFFIC_BYTES = {"llama3_8b_32k": 639_545_088, "llama3_8b_128k": 4 * 635_952_896}
 DEFAULT_WORKLOAD = "llama3_8b_32k"
 LONG_WORKLOAD = "llama3_8b_128k"
 
@@ -376,7 +378,10 @@ def measure_workload(name, args, rank, dist, device, peaks, steps, warmup, seed,
     """value/e2e/phase measurements of one workload on this rank's own sequence."""
     import xattn_b200
     from xattn_b200 import ops, synth
-    dq, dk, dv, w = synth.make_inputs(name, seed=seed, device=device)
+    dq, dk, dv, w = synth.make_inputs(name, seed=seed, device=device, heads_limit=args.heads_limit)
+    if args.heads_limit is not None:             # a kv-group slice of the workload (small captures under a profiler)
+        import dataclasses
+        w = dataclasses.replace(w, hq=dq.shape[1], hkv=dk.shape[1], name=f"{w.name}[{dk.shape[1]} kv group(s)]")
     chunk = w.chunk_size or ops.default_chunk_size(w.seq_len)
     q_pin, k_pin, v_pin = dq.cpu().pin_memory(), dk.cpu().pin_memory(), dv.cpu().pin_memory()
     out_host = torch.empty(1, w.hq, w.seq_len, w.head_dim, dtype=w.dtype).pin_memory()
@@ -735,6 +740,8 @@ def main():
                     help="only the primary workload: no long-context record, reference-on-GPU figures or extra "
                          "multi-GPU legs (for profiling runs)")
     ap.add_argument("--cpu-q-blocks", type=int, default=64)
+    ap.add_argument("--heads-limit", type=int, default=None,
+                    help="keep only the first N kv-head groups of the workload (small cases for profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":

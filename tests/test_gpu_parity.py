@@ -640,6 +640,40 @@ def test_llama_attention_core_prefill_decode_and_gqa():
     assert err.max() < OUT_MAX_ABS and err.mean() < OUT_MEAN_ABS
 
 
+def test_llama_attention_patch_matches_the_unpatched_model_at_threshold_one():
+    """A small random-weight Hugging Face Llama (2 layers, 4 query / 2 kv heads of 128) with every attention module
+    patched (projections, in-place RoPE, cache update, XAttention prefill, dense decode, o_proj): at threshold 1
+    the selection keeps every causal block, so prefill and a following decode step must reproduce the unpatched
+    model (SDPA attention) up to 16-bit rounding."""
+    transformers = pytest.importorskip("transformers")
+    from transformers import LlamaConfig, LlamaModel
+    from transformers.cache_utils import DynamicCache
+    from xattn_b200.llama_shim import FastPrefillConfig, patch_llama_attention
+    cfg = LlamaConfig(vocab_size=128, hidden_size=512, intermediate_size=1024, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=2, head_dim=128, max_position_embeddings=4096,
+                      rope_theta=500000.0, attn_implementation="sdpa")
+    torch.manual_seed(0)
+    model = LlamaModel(cfg).to(device=DEV, dtype=torch.bfloat16).eval()
+    L = 1024
+    ids = torch.randint(0, 128, (1, L + 1), device=DEV)
+    with torch.no_grad():
+        ref_cache = DynamicCache(config=cfg)
+        ref_pre = model(input_ids=ids[:, :L], past_key_values=ref_cache, use_cache=True).last_hidden_state
+        ref_dec = model(input_ids=ids[:, L:], past_key_values=ref_cache, use_cache=True).last_hidden_state
+        n = patch_llama_attention(model, FastPrefillConfig(threshold=1.0, stride=8, num_layers=2, num_heads=4,
+                                                           device=DEV))
+        assert n == 2
+        cache = DynamicCache(config=cfg)
+        got_pre = model(input_ids=ids[:, :L], past_key_values=cache, use_cache=True).last_hidden_state
+        got_dec = model(input_ids=ids[:, L:], past_key_values=cache, use_cache=True).last_hidden_state
+    import xattn_b200
+    xattn_b200.check_device_status()
+    for got, ref in ((got_pre, ref_pre), (got_dec, ref_dec)):
+        err = (got.float() - ref.float()).abs()
+        scale = ref.float().abs().mean()
+        assert err.mean() < 0.02 * scale and err.max() < 0.25 * ref.float().abs().max(), (err.mean(), err.max(), scale)
+
+
 def test_dit_varlen_wrapper_ragged_lengths():
     """The video-diffusion call pattern: a valid segment whose length is no multiple of 128 (or of the stride)
     through non-causal XAttention, a padded text tail dense; threshold >= 1 switches the first to dense."""

@@ -169,3 +169,18 @@ def test_host_pipeline_steps_keep_the_kv_head_mapping():
                     firsts += int(first)
                 assert seen == list(range(hq))
                 assert firsts == (hkv + gps - 1) // gps
+
+
+def test_default_thresholds_are_the_profiled_llama_tables():
+    """FastPrefillConfig(threshold=None) takes the per-(layer, head) table of its stride, as the reference does
+    (xattn/src/load_llama.py:253-261); the tables are data generated from xattn/threshold/llama_threshold.py."""
+    from xattn_b200.llama_shim import FastPrefillConfig, default_threshold_table
+    means = {4: 0.79205, 8: 0.76135, 16: 0.90738}
+    for stride, mean in means.items():
+        t = FastPrefillConfig(threshold=None, stride=stride, device="cpu").threshold
+        assert t.shape == (32, 32) and t.dtype == torch.float32
+        assert abs(float(t.mean()) - mean) < 1e-4 and 0.0 <= float(t.min()) and float(t.max()) <= 1.0
+        assert torch.equal(t, default_threshold_table(stride))
+    with pytest.raises(ValueError):
+        default_threshold_table(32)
+    assert float(FastPrefillConfig(threshold=0.9, device="cpu").threshold.mean()) == pytest.approx(0.9)

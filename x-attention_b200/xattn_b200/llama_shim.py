@@ -8,12 +8,18 @@ RoPE and the cache update (which stay the model's business) its core is: repeat 
 kv head h // (Hq/Hkv)), prefill goes to the sm_100a XAttention path, decode and the "full" metric run dense
 through the same block-sparse attention kernel with an all-ones block list.
 
-`FastPrefillConfig` mirrors the reference's (xattn/src/load_llama.py:224-262).  The reference ships
-per-(layer, head) threshold tables for Llama-3.1-8B (xattn/threshold/llama_threshold.py); they are model data,
-not part of this package: pass your table as `threshold` ([layers, heads] tensor) or a scalar.
+`llama_attention_forward` / `patch_llama_attention` are the whole patch for Hugging Face's `LlamaAttention`
+(projections, in-place RoPE on the projection outputs, cache update, prefill or decode core, `o_proj` fed
+without a transposed copy).
+
+`FastPrefillConfig` mirrors the reference's (xattn/src/load_llama.py:224-262), including its default: with no
+threshold given, the per-(layer, head) table the reference ships for Llama-3.1-8B and the chosen stride
+(xattn/threshold/llama_threshold.py, stored as data/llama_thresholds.npz).
 """
 from __future__ import annotations
 
+import os
+import types
 from typing import Optional, Union
 
 import torch
@@ -32,11 +38,21 @@ class FastPrefillConfig(dict):
         self.metric = metric
         self.stride = stride
         if threshold is None:
-            threshold = 0.9
+            # xattn/src/load_llama.py:253-261: the profiled Llama-3.1-8B table of the stride
+            threshold = default_threshold_table(stride)
         if isinstance(threshold, torch.Tensor):
             self.threshold = threshold.to(device=device, dtype=torch.float32)
         else:
             self.threshold = torch.ones((num_layers, num_heads), device=device) * float(threshold)
+
+
+def default_threshold_table(stride: int) -> torch.Tensor:
+    """[32, 32] per-(layer, head) thresholds the reference profiled for Llama-3.1-8B-Instruct at stride 4, 8 or 16."""
+    import numpy as np
+    if stride not in (4, 8, 16):
+        raise ValueError("the reference ships threshold tables for stride 4, 8 and 16 only")
+    z = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "data", "llama_thresholds.npz"))
+    return torch.from_numpy(z[f"fuse_{stride}"].copy())
 
 
 def _dense_lists(batch, heads, q_len, k_len, device):
@@ -84,3 +100,55 @@ def rope_and_attend(q_proj_out: torch.Tensor, k_proj_out: torch.Tensor, v_proj_o
     if not out_blhd.is_contiguous():                               # never for this package's kernels
         out_blhd = out_blhd.contiguous()
     return out_blhd.reshape(B, L, num_heads * D)
+
+
+def llama_attention_forward(self, hidden_states: torch.Tensor, position_embeddings=None, attention_mask=None,
+                            past_key_values=None, past_key_value=None, cache_position=None, **kwargs):
+    """Replacement for `LlamaAttention.forward` (what the reference's `forward_eval` does,
+    xattn/src/load_llama.py:80-220), for modules that carry a `fastprefillconfig`.  Prefill (q_len == k_len, or a
+    chunk against a longer cache) goes through XAttention with the layer's thresholds, a single new token against
+    the cache through dense attention.  The attention mask is not consulted: like the reference's path, the call
+    is causal over one un-padded sequence per batch entry.  Returns (attn_output, None)."""
+    cfg = self.fastprefillconfig
+    cache = past_key_values if past_key_values is not None else past_key_value
+    B, L, _ = hidden_states.shape
+    D = self.head_dim
+    q_out, k_out, v_out = self.q_proj(hidden_states), self.k_proj(hidden_states), self.v_proj(hidden_states)
+    Hq, Hkv = q_out.shape[-1] // D, k_out.shape[-1] // D
+    q = q_out.view(B, L, Hq, D).transpose(1, 2)
+    k = k_out.view(B, L, Hkv, D).transpose(1, 2)
+    v = v_out.view(B, L, Hkv, D).transpose(1, 2)
+    if position_embeddings is None:
+        raise ValueError("position_embeddings=(cos, sin) is required")
+    cos, sin = position_embeddings
+    if q.dtype in (torch.bfloat16, torch.float16) and q.is_cuda:
+        ops.apply_rotary_pos_emb_(q, k, cos.to(q.dtype), sin.to(q.dtype))      # in place, on the projection outputs
+    else:
+        raise TypeError("llama_attention_forward needs 16-bit CUDA activations")
+    if cache is not None:
+        try:
+            k, v = cache.update(k, v, self.layer_idx, {"sin": sin, "cos": cos, "cache_position": cache_position})
+        except TypeError:
+            k, v = cache.update(k, v, self.layer_idx)
+        if cache_position is not None and type(cache).__name__ == "StaticCache":       # load_llama.py:147-149
+            end = min(int(cache_position[-1]) + 1, k.shape[2])
+            k, v = k[:, :, :end], v[:, :, :end]
+    out = attention_core(q, k, v, self.layer_idx, cfg)                 # [B, Hq, L, D] view of [B, L, Hq, D] storage
+    out = out.transpose(1, 2)
+    if not out.is_contiguous():
+        out = out.contiguous()
+    return self.o_proj(out.reshape(B, L, Hq * D)), None
+
+
+def patch_llama_attention(model: torch.nn.Module, config: Optional[FastPrefillConfig] = None) -> int:
+    """Give every `LlamaAttention`-like module of `model` (one that has q_proj, k_proj, v_proj, o_proj, head_dim and
+    layer_idx) the forward above and `config` as its `fastprefillconfig` (the reference assigns both in
+    xattn/src/load_llama.py:265-300).  Returns the number of modules patched."""
+    cfg = config if config is not None else FastPrefillConfig()
+    n = 0
+    for m in model.modules():
+        if all(hasattr(m, a) for a in ("q_proj", "k_proj", "v_proj", "o_proj", "head_dim", "layer_idx")):
+            m.fastprefillconfig = cfg
+            m.forward = types.MethodType(llama_attention_forward, m)
+            n += 1
+    return n
