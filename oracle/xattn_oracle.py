@@ -27,10 +27,13 @@ Parity pinning
 * estimate + selection: pinned against the *unmodified reference code* imported on the CPU
   (``tests/golden/make_golden.py`` generates ``tests/golden/*.npz`` from the reference;
   ``tests/test_oracle_golden.py`` replays them through this module).
-* block-sparse attention: **parity unpinned** by the reference (no tests, no golden vectors,
-  source of the kernel absent).  The definition used is the one the reference's baseline
-  file states for this path: dense fp32 softmax(QK^T/sqrt(D)) V restricted to kept 128x128
-  blocks, token-level causal inside kept blocks when ``causal``.
+* block-sparse attention, causal: pinned against the reference's own in-tree statement of the operation,
+  ``torch_block_wise_attention`` (xattn/src/Flexprefill.py:12-44), imported on the CPU and run in fp32 on
+  seeded cases (``tests/golden/attention_blockwise.npz``; replayed by ``tests/test_oracle_golden.py``).
+  Non-causal masks and queries shorter than the keys have no reference-held statement (the production
+  kernel lives in ``block_sparse_attn==0.0.1``, whose source is not part of the reference tree): there the
+  definition is dense fp32 softmax(QK^T/sqrt(D)) V restricted to kept 128x128 blocks, query end aligned to
+  key end, checked against torch's scaled_dot_product_attention on all-ones masks.
 
 Two estimate semantics are restated (they differ only for causal, un-padded K, see
 ``estimate_block_sums``):
