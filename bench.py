@@ -336,7 +336,12 @@ def phase_profile(w, dq, dk, dv, chunk, reps, device, peaks):
 
 def attention_roofline(name, prof, peaks):
     a = prof["rooflines"]["attend"]
-    return dict(bound=a["bound"], kernel="block_sparse_attn_kernel", achieved=a["tflops"], peak=peaks["bf16"],
+    from xattn_b200 import ops, synth
+    w = synth.WORKLOADS[name]
+    split = w.seq_len // 128 >= ops.PAIR_MIN_Q_BLOCKS and w.hq // w.hkv >= 2 and (w.hq // w.hkv) % 2 == 0
+    kernel = ("block_sparse_attn_pair_kernel (rows whose kv group shares a list of one or two blocks) + "
+              "block_sparse_attn_kernel (the rest), one call") if split else "block_sparse_attn_kernel"
+    return dict(bound=a["bound"], kernel=kernel, achieved=a["tflops"], peak=peaks["bf16"],
                 unit="TFLOP/s", frac=a["frac"], hbm_achieved_gbs=a["gbs"], hbm_peak_gbs=peaks["hbm"],
                 hbm_frac=a["hbm_frac"], traffic=NCU_ATTENTION_TRAFFIC_BYTES.get(name),
                 traffic_unit="bytes per launch (ncu)", algorithmic_bytes=a["algorithmic_bytes"],

@@ -236,13 +236,20 @@ int xattn_b200_block_sparse_attn(const void* q, const void* k, const void* v, in
  * in a kernel of their own: K/V tiles loaded once per kv head and query block and shared by its query heads
  * (GQA head sharing), both Q.K^T products and both P.V products issued back to back, one softmax pass without
  * online rescaling.  Which rows qualify is decided on the device (no synchronisation); all other rows run through
- * the general kernel of xattn_b200_block_sparse_attn.  Same call-site contract (xattn/src/Xattention.py:377-391),
- * same results up to the summation order.
+ * the general kernel of xattn_b200_block_sparse_attn.  Because two kernels in a row cost a second tail, the split is
+ * also only made, again decided on the device, when the qualifying rows list at least 92 % of the call's blocks
+ * (Llama-3.1-8B at 128K tokens: 95 %, 8 % faster; at 64K: 89 %, no gain; at 32K: 66 %, a loss); below that the
+ * general kernel computes everything and the attempt has cost 30-45 microseconds (so callers with short sequences
+ * should use xattn_b200_block_sparse_attn; the Python layer offers the workspace from 96K tokens on).
+ * xattn_b200_block_sparse_attn_split_share(percent) replaces the 92 for the calls enqueued after it (0: split
+ * whenever anything qualifies, 101: never) and returns the previous value; a negative argument only reads it.
+ * Same call-site contract (xattn/src/Xattention.py:377-391), same results up to the summation order.
  * workspace: device memory of xattn_b200_block_sparse_attn_workspace_bytes() bytes, 16-byte aligned, contents
  * irrelevant on entry; the call's kernels use it until they finish.  A size of 0 means the shape gains nothing
  * (hq / hkv odd or 1) and the call equals xattn_b200_block_sparse_attn; NULL is then accepted.
  */
 size_t xattn_b200_block_sparse_attn_workspace_bytes(int batch, int hq, int hkv, int q_len, int k_len);
+int xattn_b200_block_sparse_attn_split_share(int percent);
 int xattn_b200_block_sparse_attn_ws(const void* q, const void* k, const void* v, int dtype, int batch, int hq, int hkv,
                                     int q_len, int k_len, int head_dim, int64_t q_stride_b, int64_t q_stride_h,
                                     int64_t q_stride_l, int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_l,

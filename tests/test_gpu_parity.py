@@ -284,13 +284,47 @@ def test_short_shared_lists_take_the_pair_kernel(causal, dtype, hq, hkv, lq, lk)
         mask[0, :, 5, :] = False
         mask[0, :, 5, min(off + 5, kb - 1)] = True      # a one-block list shared by all heads
     idx, cnt = ops.mask_to_lists(mask.to(DEV), lq, lk, causal)
-    out = ops.block_sparse_attention(q.to(DEV), k.to(DEV), v.to(DEV), idx, cnt, causal,
-                                     use_pair_kernel=True).float().cpu()
+    # these small masks stay below the share of qualifying blocks at which the library splits a call by itself
+    before = ops.pair_split_share(0)
+    try:
+        n0 = ops._lib.load().xattn_b200_launch_count()
+        out = ops.block_sparse_attention(q.to(DEV), k.to(DEV), v.to(DEV), idx, cnt, causal,
+                                         use_pair_kernel=True).float().cpu()
+        assert ops._lib.load().xattn_b200_launch_count() - n0 == 3      # classify, pair kernel, general kernel
+    finally:
+        ops.pair_split_share(before)
     ref = orc.block_sparse_attention_oracle(q, k, v, mask, causal)
     err = (out - ref).abs()
     assert err.max() < OUT_MAX_ABS and err.mean() < OUT_MEAN_ABS, (err.max(), err.mean())
     gen = ops.block_sparse_attention(q.to(DEV), k.to(DEV), v.to(DEV), idx, cnt, causal, use_pair_kernel=False)
     _assert_same_up_to_body_choice(out, gen.float().cpu())
+
+
+def test_pair_kernel_is_declined_on_the_device_when_few_blocks_qualify():
+    """With the library's own rule (92 % of the listed blocks must qualify) a mask whose rows mostly list three blocks
+    is computed by the general kernel alone, although the pair kernel was offered its scratch memory: same output as
+    without it, bit for bit; a sink + diagonal mask takes the split and matches up to summation order."""
+    from xattn_b200 import ops
+    assert ops.pair_split_share() == 92
+    g = torch.Generator().manual_seed(5)
+    hq, hkv, L = 8, 2, 4096
+    q = torch.randn(1, hq, L, 128, generator=g).bfloat16().to(DEV)
+    k = torch.randn(1, hkv, L, 128, generator=g).bfloat16().to(DEV)
+    v = torch.randn(1, hkv, L, 128, generator=g).bfloat16().to(DEV)
+    nb = L // 128
+    eye = torch.eye(nb, dtype=torch.bool)
+    two = eye.clone(); two[:, 0] = True
+    three = two | torch.diag(torch.ones(nb - 1, dtype=torch.bool), -1)
+    for base, split in ((three, False), (two, True)):
+        mask = base[None, None].expand(1, hq, -1, -1).contiguous()
+        idx, cnt = ops.mask_to_lists(mask.to(DEV), L, L, True)
+        gen = ops.block_sparse_attention(q, k, v, idx, cnt, True, use_pair_kernel=False).clone()
+        both = ops.block_sparse_attention(q, k, v, idx, cnt, True, use_pair_kernel=True)
+        if split:
+            assert not torch.equal(both, gen)                      # another summation order: the pair kernel ran
+            _assert_same_up_to_body_choice(both.float().cpu(), gen.float().cpu())
+        else:
+            assert torch.equal(both, gen)
 
 
 @pytest.mark.parametrize("causal,density,hq,hkv,L", [(True, 1.0, 2, 1, 4096), (False, 0.5, 2, 2, 3072), (True, 0.3, 4, 2, 5000)])

@@ -20,6 +20,7 @@ SIGNATURES = {
     "xattn_b200_version": (_i, []),
     "xattn_b200_error_string": (C.c_char_p, [_i]),
     "xattn_b200_launch_count": (C.c_ulonglong, []),
+    "xattn_b200_block_sparse_attn_split_share": (_i, [_i]),
     "xattn_b200_default_chunk_size": (_i, [_i]),
     "xattn_b200_estimate_geometry": (_i, [_i, _i, _i, _i, _i, C.POINTER(_i)]),
     "xattn_b200_estimate_workspace_bytes": (_sz, [_i, _i, _i, _i, _i, _i, _i]),

@@ -26,6 +26,7 @@ int block_sparse_attn_launch(const void* q, const void* k, const void* v, int dt
                              int64_t osb, int64_t osh, int64_t osl, void* workspace, size_t workspace_bytes,
                              int* status, cudaStream_t stream);
 size_t block_sparse_attn_workspace_bytes(int batch, int hq, int hkv, int q_len, int k_len);
+int pair_min_share_pct(int set_to);
 }  // namespace xb
 
 extern "C" {
@@ -146,6 +147,8 @@ int xattn_b200_block_sparse_attn(const void* q, const void* k, const void* v, in
                                       v_stride_l, block_idx, block_cnt, causal, scale, out, o_stride_b, o_stride_h,
                                       o_stride_l, nullptr, 0, status, static_cast<cudaStream_t>(cuda_stream));
 }
+
+int xattn_b200_block_sparse_attn_split_share(int percent) { return xb::pair_min_share_pct(percent); }
 
 size_t xattn_b200_block_sparse_attn_workspace_bytes(int batch, int hq, int hkv, int q_len, int k_len) {
   return xb::block_sparse_attn_workspace_bytes(batch, hq, hkv, q_len, k_len);

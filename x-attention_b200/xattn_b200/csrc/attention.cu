@@ -31,6 +31,8 @@
 // [256,384) O of stream 0, [384,512) O of stream 1.
 #include <math.h>
 
+#include <atomic>
+
 #include "attention_common.cuh"
 
 namespace xb {
@@ -857,8 +859,14 @@ block_sparse_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
                          const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmKf,
                          const __grid_constant__ CUtensorMap tmVf, const AttnParams p,
                          const int32_t* __restrict__ block_idx, const int32_t* __restrict__ block_cnt,
-                         void* __restrict__ out, int* status) {
+                         const int32_t* __restrict__ cnt_rest, const int* __restrict__ pair_header,
+                         int pair_min_share, void* __restrict__ out, int* status) {
   extern __shared__ __align__(1024) uint8_t smem[];
+  // with a pair kernel in front: its leftovers if it ran, the original counts if it declined.  In that case this
+  // kernel was launched while the pair kernel was running and first waits for it (and so for the classify kernel
+  // before it) to end.
+  pdl_wait();
+  if (cnt_rest && pair_path_chosen(pair_header, pair_min_share)) block_cnt = cnt_rest;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   if ((smem_u32(smem) & 1023u) != 0) {              // the swizzled tiles need 1024-byte alignment
@@ -907,8 +915,15 @@ size_t pair_workspace_bytes(int batch, int hq, int hkv, int q_len);
 bool pair_path_applies(int hq, int hkv, int k_len);
 int block_sparse_attn_pair_launch(const CUtensorMap& tmQ, const CUtensorMap& tmKf, const CUtensorMap& tmVf,
                                   const AttnParams& p, const int32_t* block_idx, const int32_t* block_cnt, void* out,
-                                  void* workspace, size_t workspace_bytes, const int32_t** cnt_rest, int* status,
-                                  cudaStream_t stream);
+                                  void* workspace, size_t workspace_bytes, const int32_t** cnt_rest,
+                                  const int** header, int min_share_pct, int* status, cudaStream_t stream);
+
+// Share (per cent) of a call's listed blocks that must qualify for the pair kernel before the call is split; a
+// process-wide setting, read when a call is enqueued.  0: split whenever anything qualifies; > 100: never.
+static std::atomic<int> g_pair_min_share{kPairMinSharePct};
+int pair_min_share_pct(int set_to) {
+  return set_to < 0 ? g_pair_min_share.load() : g_pair_min_share.exchange(set_to);
+}
 
 size_t block_sparse_attn_workspace_bytes(int batch, int hq, int hkv, int q_len, int k_len) {
   if (batch < 1 || hq < 1 || hkv < 1 || hq % hkv != 0 || q_len < 1 || k_len < 1) return 0;
@@ -955,15 +970,19 @@ int block_sparse_attn_launch(const void* q, const void* k, const void* v, int dt
   const int sms = sm_count();
   const int grid = items < sms ? static_cast<int>(items) : sms;
   if ((items + grid - 1) / grid > kSchedCap || p.list_k_blocks > 65534) return XATTN_B200_ERR_LIMIT;
+  const int32_t* rest = nullptr;
+  const int* pair_header = nullptr;
+  const int min_share = g_pair_min_share.load();
   if (workspace && pair_path_applies(hq, hkv, k_len)) {
-    const int32_t* rest = nullptr;
     if ((rc = block_sparse_attn_pair_launch(tmQ, tmKf, tmVf, p, block_idx, block_cnt, out, workspace, workspace_bytes,
-                                            &rest, status, stream)))
+                                            &rest, &pair_header, min_share, status, stream)))
       return rc;
-    block_cnt = rest;
   }
+  if (rest)
+    return launch_dependent(block_sparse_attn_kernel, dim3(grid), dim3(kAttnThreads), kAttnSmem, stream, tmQ, tmK, tmV,
+                            tmKf, tmVf, p, block_idx, block_cnt, rest, pair_header, min_share, out, status);
   block_sparse_attn_kernel<<<grid, kAttnThreads, kAttnSmem, stream>>>(tmQ, tmK, tmV, tmKf, tmVf, p, block_idx, block_cnt,
-                                                                      out, status);
+                                                                      rest, pair_header, min_share, out, status);
   return launch_status();
 }
 

@@ -17,18 +17,20 @@
 //     [128,256).  P_a (16 bit) overwrites columns [0,64) of S_a in ascending chunk order and P_b columns
 //     [192,256) of S_b in descending chunk order (each P chunk lands on S columns that are in registers
 //     already), which leaves the 128 columns [64,192) in the middle for O once the softmax has read them.
-//   * The softmax warpgroup of a stream also normalises its output and hands it to TMA stores (it owns the rows
-//     and is idle while its P.V runs), so there is no epilogue warpgroup and a softmax thread may use ~220
-//     registers.
+//   * A stream has TWO softmax warpgroups, one per block: each thread owns one row of ONE block (128 columns), the
+//     row maxima of the two blocks are exchanged through shared memory, and the second warpgroup (the diagonal
+//     block, which has less to exponentiate) also normalises the output and hands it to TMA stores.  Four softmax
+//     warps per scheduler instead of two: a softmax warp runs at the instruction rate of a single warp (dependent
+//     chains behind tensor-memory loads), so the schedulers were two thirds idle.
 //   * The two streams run half a round apart on purpose: stream 1 issues its Q.K^T when stream 0 has finished
 //     its first softmax pass, and stream 0 issues its next Q.K^T when that one has completed.  Left alone both streams fall into
 //     lockstep (both in their MMA phase, then both exponentiating on the same special-function units, each at
 //     half speed); kept apart, one stream's MMAs run under the other's softmax.
 //
-//   warps 0-3   softmax + output of stream 0 }  one thread per query row
-//   warps 4-7   softmax + output of stream 1 }
-//   warp  8     TMA loader (lane 0): K_a, K_b, V_a, V_b per group item, Q per (round, stream)
-//   warp  9/11  tcgen05 issuer of stream 0 / 1 (lane 0)
+//   warps 0-3 / 4-7     stream 0: softmax of block a / softmax of block b + output   } one thread per query row
+//   warps 8-11 / 12-15  stream 1: the same                                            } and block
+//   warp  16            TMA loader (lane 0): K_a, K_b, V_a, V_b per group item, Q per (round, stream)
+//   warp  17/19         tcgen05 issuer of stream 0 / 1 (lane 0)
 //
 // Which group items qualify is decided on the device by pair_classify_kernel (no host synchronisation): it
 // compacts them into a list and marks their items as taken in a copy of the block counts, which the general
@@ -37,12 +39,14 @@
 
 namespace xb {
 
-constexpr int kPairThreads = 384;
-constexpr int kPairLaunchRegs = 168;                      // 65536 / 384, rounded down to a multiple of 8
-constexpr int kPairSchedCap = 256;                        // group items one CTA handles per launch
+constexpr int kPairThreads = 640;
+constexpr int kPairLaunchRegs = 96;                       // 65536 / 640, rounded down to a multiple of 8
+constexpr int kPairSchedCap = 64;                         // group items one CTA handles per launch
 constexpr int kPairSmemTiles = kTile16 * 6;               // Q0, Q1, K_a, K_b, V_a, V_b
-constexpr int kPairStage = 8 * 32 * 128;                  // per softmax warp: 32 rows x 64 16-bit columns
-constexpr int kPairSmem = kPairSmemTiles + kPairStage + kPairSchedCap * 8 + 256;
+constexpr int kPairStage = 8 * 32 * 128;                  // per output warp: 32 rows x 64 16-bit columns
+constexpr int kPairXchg = 2 * 2 * 128 * 4;                // [stream][block][row] floats exchanged between warpgroups
+constexpr int kPairSmem = kPairSmemTiles + kPairStage + kPairXchg + kPairSchedCap * 8 + 256;
+static_assert(kPairSmem <= 232448, "shared memory of one CTA");
 constexpr uint32_t kNoBlock = 0xFFFFu;
 
 struct PairEntry {
@@ -58,34 +62,50 @@ __global__ void pair_classify_kernel(const int32_t* __restrict__ block_idx, cons
                                      int batch, int hq, int hkv, int q_blocks, int list_k_blocks,
                                      PairEntry* __restrict__ list, int* __restrict__ counter,
                                      int32_t* __restrict__ cnt_rest) {
+  pdl_launch_dependents();          // the pair kernel's CTAs may take their places; they wait for this grid to end
   const int units = batch * hkv * q_blocks;
   const int u = blockIdx.x * blockDim.x + threadIdx.x;
-  if (u >= units) return;
-  const int group = hq / hkv;
-  const int qb = u % q_blocks;
-  const int bg = u / q_blocks;
-  const int g = bg % hkv, b = bg / hkv;
-  const size_t row0 = (static_cast<size_t>(b) * hq + static_cast<size_t>(g) * group) * q_blocks + qb;
-  const int c0 = __ldg(block_cnt + row0);
-  bool ok = c0 == 1 || c0 == 2;
-  int i0 = 0, i1 = 0;
-  if (ok) {
-    i0 = __ldg(block_idx + row0 * list_k_blocks);
-    i1 = c0 == 2 ? __ldg(block_idx + row0 * list_k_blocks + 1) : 0;
-    for (int j = 1; j < group && ok; ++j) {
-      const size_t row = row0 + static_cast<size_t>(j) * q_blocks;
-      ok = __ldg(block_cnt + row) == c0 && __ldg(block_idx + row * list_k_blocks) == i0 &&
-           (c0 == 1 || __ldg(block_idx + row * list_k_blocks + 1) == i1);
+  int total = 0, taken = 0;
+  if (u < units) {
+    const int group = hq / hkv;
+    const int qb = u % q_blocks;
+    const int bg = u / q_blocks;
+    const int g = bg % hkv, b = bg / hkv;
+    const size_t row0 = (static_cast<size_t>(b) * hq + static_cast<size_t>(g) * group) * q_blocks + qb;
+    const int c0 = __ldg(block_cnt + row0);
+    bool ok = c0 == 1 || c0 == 2;
+    int i0 = 0, i1 = 0;
+    if (ok) {
+      i0 = __ldg(block_idx + row0 * list_k_blocks);
+      i1 = c0 == 2 ? __ldg(block_idx + row0 * list_k_blocks + 1) : 0;
+      for (int j = 1; j < group && ok; ++j) {
+        const size_t row = row0 + static_cast<size_t>(j) * q_blocks;
+        ok = __ldg(block_cnt + row) == c0 && __ldg(block_idx + row * list_k_blocks) == i0 &&
+             (c0 == 1 || __ldg(block_idx + row * list_k_blocks + 1) == i1);
+      }
     }
+    if (ok) {
+      const int pos = atomicAdd(counter, 1);
+      list[pos].unit = u;
+      list[pos].blocks = static_cast<uint32_t>(i0) | ((c0 == 2 ? static_cast<uint32_t>(i1) : kNoBlock) << 16);
+    }
+    for (int j = 0; j < group; ++j) {
+      const size_t row = row0 + static_cast<size_t>(j) * q_blocks;
+      const int c = __ldg(block_cnt + row);
+      cnt_rest[row] = ok ? -1 : c;
+      total += c;
+    }
+    taken = ok ? total : 0;
   }
-  if (ok) {
-    const int pos = atomicAdd(counter, 1);
-    list[pos].unit = u;
-    list[pos].blocks = static_cast<uint32_t>(i0) | ((c0 == 2 ? static_cast<uint32_t>(i1) : kNoBlock) << 16);
+  // block totals for pair_path_chosen(): one atomic per warp and word
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    total += __shfl_xor_sync(0xffffffffu, total, o);
+    taken += __shfl_xor_sync(0xffffffffu, taken, o);
   }
-  for (int j = 0; j < group; ++j) {
-    const size_t row = row0 + static_cast<size_t>(j) * q_blocks;
-    cnt_rest[row] = ok ? -1 : __ldg(block_cnt + row);
+  if ((threadIdx.x & 31) == 0 && total > 0) {
+    atomicAdd(reinterpret_cast<unsigned long long*>(counter + kPairTotalAll), static_cast<unsigned long long>(total));
+    atomicAdd(reinterpret_cast<unsigned long long*>(counter + kPairTotalTaken), static_cast<unsigned long long>(taken));
   }
 }
 
@@ -101,9 +121,9 @@ block_sparse_attn_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __g
                               const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
                               const AttnParams p,
                               const PairEntry* __restrict__ list, const int* __restrict__ counter, int list_offset,
-                              void* __restrict__ out, int* status) {
-  constexpr int kRegSoftmax = 224, kRegOther = 56;                  // 8 x 224 + 4 x 56 = 2016 = 12 x 168
-  static_assert(8 * kRegSoftmax + 4 * kRegOther <= 12 * kPairLaunchRegs, "register budget of the roles");
+                              int min_share_pct, void* __restrict__ out, int* status) {
+  constexpr int kRegSoftmax = 104, kRegOther = 64;                  // 16 x 104 + 4 x 64 = 1920 = 20 x 96
+  static_assert(16 * kRegSoftmax + 4 * kRegOther <= 20 * kPairLaunchRegs, "register budget of the roles");
   extern __shared__ __align__(1024) uint8_t smem[];
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -111,14 +131,22 @@ block_sparse_attn_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __g
     if (threadIdx.x == 0 && status) atomicExch(status, static_cast<int>(kDevBadSmemAlign));
     return;
   }
+  // launched while the classify kernel (or this kernel's previous window) may still run: let the next kernel of the
+  // stream queue up behind this one in the same way, then wait for what the earlier ones wrote
+  pdl_launch_dependents();
+  pdl_wait();
+  if (!pair_path_chosen(counter, min_share_pct)) return;           // the general kernel computes everything (same test there)
   // tiles: Q0, Q1, K_a, K_b, V_a, V_b
   uint8_t* stage_base = smem + kPairSmemTiles;
-  PairEntry* sch = reinterpret_cast<PairEntry*>(smem + kPairSmemTiles + kPairStage);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kPairSmemTiles + kPairStage + kPairSchedCap * 8);
+  float* xchg = reinterpret_cast<float*>(smem + kPairSmemTiles + kPairStage);          // [stream][block][row]
+  PairEntry* sch = reinterpret_cast<PairEntry*>(smem + kPairSmemTiles + kPairStage + kPairXchg);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kPairSmemTiles + kPairStage + kPairXchg + kPairSchedCap * 8);
   // GO0: stream 1's Q.K^T of a round has completed (stream 0 may issue its next one); GO1: stream 0 has the row
   // maxima of a round (stream 1 may issue its Q.K^T of that round)
+  // XCH1: both warpgroups of a stream have written their block's row maxima; XCH2: both have read them (the slot of
+  // block a then carries block a's row sums to the output warpgroup)
   enum { K_FULL = 0, K_EMPTY, V_FULL, V_EMPTY, GO0, GO1, PER_STREAM,
-         Q_FULL = 0, Q_EMPTY, S_FULL, P_READY, O_FULL, TMEM_FREE, NSTREAM };
+         Q_FULL = 0, Q_EMPTY, S_FULL, P_READY, O_FULL, TMEM_FREE, XCH1, XCH2, NSTREAM };
   const uint32_t bar0 = smem_u32(bars);
   auto gbar = [&](int which) -> uint32_t { return bar0 + 8u * which; };
   auto sbar = [&](int s, int which) -> uint32_t { return bar0 + 8u * (PER_STREAM + NSTREAM * s + which); };
@@ -126,8 +154,9 @@ block_sparse_attn_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __g
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 #ifdef XB_TRACE
   uint32_t trace_n = 0;
-  const int trace_role = warp < 8 ? ((warp & 3) == 0 ? 2 + (warp >> 2) : 7 + 3 * (warp >> 2) + (warp & 3) - 1)
-                                  : (warp == 8 ? 0 : (warp == 9 ? 1 : (warp == 11 ? 6 : 5)));
+  // softmax warps: quad 0 of (stream, block) -> 2..5, quad 3 -> 7..10, the others share 13
+  const int trace_role = warp < 16 ? ((warp & 3) == 0 ? 2 + (warp >> 2) : ((warp & 3) == 3 ? 7 + (warp >> 2) : 13))
+                                   : (warp == 16 ? 0 : (warp == 17 ? 1 : (warp == 19 ? 6 : 11)));
 #endif
 
   // this launch's share of the list: entries list_offset + blockIdx.x + i * gridDim.x, at most kPairSchedCap
@@ -148,14 +177,16 @@ block_sparse_attn_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __g
     mbar_init(gbar(V_FULL), 1);
     mbar_init(gbar(V_EMPTY), 2);
     mbar_init(gbar(GO0), 1);
-    mbar_init(gbar(GO1), 128);
+    mbar_init(gbar(GO1), 256);
     for (int s = 0; s < 2; ++s) {
       mbar_init(sbar(s, Q_FULL), 1);
       mbar_init(sbar(s, Q_EMPTY), 1);
       mbar_init(sbar(s, S_FULL), 1);
-      mbar_init(sbar(s, P_READY), 128);
+      mbar_init(sbar(s, P_READY), 256);
       mbar_init(sbar(s, O_FULL), 1);
       mbar_init(sbar(s, TMEM_FREE), 128);
+      mbar_init(sbar(s, XCH1), 256);
+      mbar_init(sbar(s, XCH2), 256);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -164,7 +195,7 @@ block_sparse_attn_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __g
     tma_prefetch_desc(&tmV);
     tma_prefetch_desc(&tmO);
   }
-  if (warp == 9) {
+  if (warp == 17) {
     tmem_alloc(smem_u32(tmem_slot), 512);
     tmem_relinquish();
   }
@@ -181,9 +212,9 @@ block_sparse_attn_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __g
     b = bg / p.hkv;
   };
 
-  if (warp >= 8) {
+  if (warp >= 16) {
     reg_set_from<kRegOther, kPairLaunchRegs>();
-    if (warp == 8) {
+    if (warp == 16) {
       // ------------------------------------------------------------------------------------- TMA loader
       if (lane == 0) {
         uint32_t rc = 0;                             // rounds so far (both streams advance together here)
@@ -235,9 +266,9 @@ block_sparse_attn_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __g
           }
         }
       }
-    } else if ((warp == 9 || warp == 11) && lane == 0) {
+    } else if ((warp == 17 || warp == 19) && lane == 0) {
       // ------------------------------------------------------------------------------------- MMA issuer of stream s
-      const int s = warp == 9 ? 0 : 1;
+      const int s = warp == 17 ? 0 : 1;
       const uint32_t idesc_qk = make_idesc_f16(128, 128, p.is_bf16 != 0, false, false);
       const uint32_t idesc_pv = make_idesc_f16(128, 128, p.is_bf16 != 0, false, true);
       const uint32_t sa = tmem_base + s * 256, sb2 = sa + 128;             // S_a / S_b
@@ -290,16 +321,22 @@ block_sparse_attn_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __g
       }
     }
   } else {
-    // --------------------------------------------------------------------------------------- softmax + output of stream s
+    // --------------------------------------------------------------------------------------- softmax (+ output)
     reg_set_from<kRegSoftmax, kPairLaunchRegs>();
-    const int s = warp >> 2;
+    const int s = warp >> 3;                                           // stream
+    const int blk = (warp >> 2) & 1;                                   // this warpgroup's block: 0 = a, 1 = b
     const int quad = warp & 3;
     const int rr = quad * 32 + lane;                                   // query row inside the block
     const uint32_t lane_bits = static_cast<uint32_t>(quad * 32) << 16;
-    const uint32_t ts = tmem_base + s * 256 + lane_bits;               // S_a of this stream, this row; S_b at +128
+    const uint32_t ts = tmem_base + s * 256 + lane_bits;               // the stream's 256 columns, this row
+    const uint32_t tS = ts + blk * 128;                                // S of this warpgroup's block
+    const uint32_t tP = ts + blk * 192;                                // its P: [0,64) for a, [192,256) for b
     const int k_off = p.k_len - p.q_len;
     const unsigned long long scale2 = pack_f32x2(p.scale_log2, p.scale_log2);
-    uint8_t* stg = stage_base + warp * (32 * 128);
+    float* x_own = xchg + (s * 2 + blk) * 128 + rr;
+    float* x_other = xchg + (s * 2 + (blk ^ 1)) * 128 + rr;
+    float* x_a = xchg + (s * 2) * 128 + rr;                            // after XCH2: block a's row sum
+    uint8_t* stg = stage_base + (s * 4 + quad) * (32 * 128);           // output warps only
     uint32_t rc = 0;
     bool ok = true;
     for (int i = 0; i < n_local && ok; ++i) {
@@ -307,29 +344,23 @@ block_sparse_attn_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __g
       int b, g, qb;
       decode(e, b, g, qb);
       const int n = (e.blocks >> 16) == kNoBlock ? 1 : 2;
-      const int k0a = static_cast<int>(e.blocks & 0xFFFFu) * 128, k0b = static_cast<int>(e.blocks >> 16) * 128;
+      const int k0 = static_cast<int>(blk == 0 ? (e.blocks & 0xFFFFu) : (e.blocks >> 16)) * 128;
       const int q_pos = qb * 128 + rr;
       int row_last = p.k_len - 1;                       // last key position this row may see
       if (p.causal && q_pos + k_off < row_last) row_last = q_pos + k_off;
-      // per block: the visible chunks are a prefix [0, nv) (visibility only ever ends towards higher columns);
-      // bit c of `mixed` = some row of the warp sees only part of chunk c
-      const int lim_a = row_last - k0a, lim_b = row_last - k0b;
-      int nv_a = 0, nv_b = 0;
-      uint32_t mixed_a = 0u, mixed_b = 0u;
+      // the visible chunks of the block are a prefix [0, nv) (visibility only ever ends towards higher columns);
+      // bit c of `mixed` = some row of the warp sees only part of chunk c.  No second block: nothing visible.
+      const int lim = row_last - k0;
+      int nv = 0;
+      uint32_t mixed = 0u;
+      if (blk < n) {
 #pragma unroll
-      for (int c4 = 0; c4 < 4; ++c4) {
-        const bool all_a = __all_sync(0xffffffffu, lim_a - 32 * c4 >= 31);
-        const bool none_a = __all_sync(0xffffffffu, lim_a - 32 * c4 < 0);
-        if (!none_a) {
-          nv_a = c4 + 1;
-          if (!all_a) mixed_a |= 1u << c4;
-        }
-        if (n == 2) {
-          const bool all_b = __all_sync(0xffffffffu, lim_b - 32 * c4 >= 31);
-          const bool none_b = __all_sync(0xffffffffu, lim_b - 32 * c4 < 0);
-          if (!none_b) {
-            nv_b = c4 + 1;
-            if (!all_b) mixed_b |= 1u << c4;
+        for (int c4 = 0; c4 < 4; ++c4) {
+          const bool all_v = __all_sync(0xffffffffu, lim - 32 * c4 >= 31);
+          const bool none_v = __all_sync(0xffffffffu, lim - 32 * c4 < 0);
+          if (!none_v) {
+            nv = c4 + 1;
+            if (!all_v) mixed |= 1u << c4;
           }
         }
       }
@@ -339,113 +370,70 @@ block_sparse_attn_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __g
         if (!__all_sync(0xffffffffu, mbar_wait(sbar(s, S_FULL), rc & 1, abort_flag))) { ok = false; break; }
         tc_fence_after();
         if (lane == 0) XB_TRACE_EV(0x31, rc);
-        // ---- pass 1: row maximum over the visible columns of both blocks (8 chains of 3-input max).  A block is
-        // read with all its visible chunks in flight and one wait.  Block b goes first and is dropped; block a
-        // (for a causal list the sink, all of it visible) stays in registers for pass 2, so tensor memory is
-        // read three times per two blocks, not four.
+        // ---- pass 1: row maximum over the visible columns of this block (8 chains of 3-input max), two
+        // tensor-memory loads in flight per wait
         float mx8[8];
 #pragma unroll
         for (int q = 0; q < 8; ++q) mx8[q] = -INFINITY;
-        auto max32 = [&](const uint32_t (&v)[32], int rot) {
+#pragma unroll 1
+        for (int c2 = 0; c2 < 2 && 2 * c2 < nv; ++c2) {
+          uint32_t v0[32], v1[32];
+          const bool two = 2 * c2 + 1 < nv;
+          tmem_ld32(tS + c2 * 64, v0);
+          if (two) tmem_ld32(tS + c2 * 64 + 32, v1);
+          tc_wait_ld();
+          if ((mixed >> (2 * c2)) & 1u) mask_chunk(v0, lim - 64 * c2);
 #pragma unroll
           for (int k = 0; k < 16; ++k)
-            mx8[(k + rot) & 7] = max3(mx8[(k + rot) & 7], __uint_as_float(v[2 * k]), __uint_as_float(v[2 * k + 1]));
-        };
-        uint32_t a0[32], a1[32], a2[32], a3[32];
-        if (n == 2) {
-          const uint32_t tb = ts + 128;
-          if (nv_b > 0) tmem_ld32(tb, a0);
-          if (nv_b > 1) tmem_ld32(tb + 32, a1);
-          if (nv_b > 2) tmem_ld32(tb + 64, a2);
-          if (nv_b > 3) tmem_ld32(tb + 96, a3);
-          tc_wait_ld();
-          if (mixed_b) {
-            if (mixed_b & 1u) mask_chunk(a0, lim_b);
-            if (mixed_b & 2u) mask_chunk(a1, lim_b - 32);
-            if (mixed_b & 4u) mask_chunk(a2, lim_b - 64);
-            if (mixed_b & 8u) mask_chunk(a3, lim_b - 96);
+            mx8[k & 7] = max3(mx8[k & 7], __uint_as_float(v0[2 * k]), __uint_as_float(v0[2 * k + 1]));
+          if (two) {
+            if ((mixed >> (2 * c2 + 1)) & 1u) mask_chunk(v1, lim - 64 * c2 - 32);
+#pragma unroll
+            for (int k = 0; k < 16; ++k)
+              mx8[(k + 4) & 7] = max3(mx8[(k + 4) & 7], __uint_as_float(v1[2 * k]), __uint_as_float(v1[2 * k + 1]));
           }
-          if (nv_b > 0) max32(a0, 0);
-          if (nv_b > 1) max32(a1, 4);
-          if (nv_b > 2) max32(a2, 0);
-          if (nv_b > 3) max32(a3, 4);
         }
-        if (nv_a > 0) tmem_ld32(ts, a0);
-        if (nv_a > 1) tmem_ld32(ts + 32, a1);
-        if (nv_a > 2) tmem_ld32(ts + 64, a2);
-        if (nv_a > 3) tmem_ld32(ts + 96, a3);
-        tc_wait_ld();
-        if (mixed_a) {
-          if (mixed_a & 1u) mask_chunk(a0, lim_a);
-          if (mixed_a & 2u) mask_chunk(a1, lim_a - 32);
-          if (mixed_a & 4u) mask_chunk(a2, lim_a - 64);
-          if (mixed_a & 8u) mask_chunk(a3, lim_a - 96);
-        }
-        if (nv_a > 0) max32(a0, 0);
-        if (nv_a > 1) max32(a1, 4);
-        if (nv_a > 2) max32(a2, 0);
-        if (nv_a > 3) max32(a3, 4);
-        const float mx = fmaxf(max3(mx8[0], mx8[1], mx8[2]), max3(max3(mx8[3], mx8[4], mx8[5]), mx8[6], mx8[7]));
+        float mx = fmaxf(max3(mx8[0], mx8[1], mx8[2]), max3(max3(mx8[3], mx8[4], mx8[5]), mx8[6], mx8[7]));
+        // the row's maximum over both blocks: through shared memory, with the other warpgroup of the stream
+        *x_own = mx;
+        mbar_arrive(sbar(s, XCH1));
+        if (!__all_sync(0xffffffffu, mbar_wait(sbar(s, XCH1), rc & 1, abort_flag))) { ok = false; break; }
+        mx = fmaxf(mx, *x_other);
+        mbar_arrive(sbar(s, XCH2));                                    // this thread has read the other's maximum
+        if (s == 0) mbar_arrive(gbar(GO1));            // stream 1 may issue its Q.K^T: it runs under this stream's pass 2
         const float m_ref = mx == -INFINITY ? 0.f : mx * p.scale_log2;
-        if (s == 0) mbar_arrive(gbar(GO1));           // stream 1 may issue its Q.K^T: it runs under this stream's pass 2
         if (lane == 0) XB_TRACE_EV(0x35, rc);
-        // ---- pass 2: P = exp2(S * scale - m) in 32-column chunks.  Block a from the registers, P chunk c to
-        // columns [16 c, 16 c + 16) of S_a.  Block b is read again, chunks descending with the next load in flight,
-        // P chunk c to columns [64 + 16 c, 64 + 16 c + 16) of S_b: a P chunk overwrites only S columns that have
-        // been read (or are invisible).
+        // ---- pass 2: P = exp2(S * scale - m) in 32-column chunks.  Block a ascending, P chunk c to columns
+        // [16 c, 16 c + 16) of S_a; block b descending, P chunk c to columns [64 + 16 c, 64 + 16 c + 16) of S_b:
+        // either way a P chunk overwrites only S columns that have been read (or are invisible).
         const unsigned long long nmref2 = pack_f32x2(-m_ref, -m_ref);
         unsigned long long ls2[4];
 #pragma unroll
         for (int q = 0; q < 4; ++q) ls2[q] = 0ull;     // (+0.f, +0.f)
-        auto exp32 = [&](const uint32_t (&v)[32], uint32_t taddr) {      // 32 scores -> 16 packed columns of P
-          uint32_t pk[16];
-#pragma unroll
-          for (int k = 0; k < 16; ++k) {
-            float y0, y1;
-            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(v[2 * k]), __uint_as_float(v[2 * k + 1])), scale2, nmref2),
-                         y0, y1);
-            const float p0 = fast_exp2(y0), p1 = fast_exp2(y1);
-            ls2[k & 3] = add_f32x2(ls2[k & 3], pack_f32x2(p0, p1));
-            pk[k] = pack16(p0, p1, p.is_bf16);
-          }
-          tmem_st16(taddr, pk);
-        };
-        auto zero16 = [&](uint32_t taddr) {
-          uint32_t pk[16];
-#pragma unroll
-          for (int k = 0; k < 16; ++k) pk[k] = 0u;
-          tmem_st16(taddr, pk);
-        };
-        if (nv_a > 0) exp32(a0, ts); else zero16(ts);
-        if (nv_a > 1) exp32(a1, ts + 16); else zero16(ts + 16);
-        if (nv_a > 2) exp32(a2, ts + 32); else zero16(ts + 32);
-        if (nv_a > 3) exp32(a3, ts + 48); else zero16(ts + 48);
-        if (n == 2) {
-          const uint32_t tb = ts + 128, tp = ts + 192;
-          // chunks 3, 2, 1, 0: buffers a0/a1 alternate, the next visible chunk is requested before the current one
-          // is exponentiated
-          if (3 < nv_b) tmem_ld32(tb + 96, a0);
+        if (blk < n) {
 #pragma unroll 1
-          for (int c2 = 0; c2 < 2; ++c2) {
-            const int cA = 3 - 2 * c2, cB = 2 - 2 * c2;
-            if (cA < nv_b) {
+          for (int kk = 0; kk < 4; ++kk) {
+            const int c4 = blk == 0 ? kk : 3 - kk;
+            uint32_t pk[16];
+            if (c4 < nv) {
+              uint32_t v[32];
+              tmem_ld32(tS + c4 * 32, v);
               tc_wait_ld();
-              if (cB < nv_b) tmem_ld32(tb + cB * 32, a1);
-              if ((mixed_b >> cA) & 1u) mask_chunk(a0, lim_b - 32 * cA);
-              exp32(a0, tp + cA * 16);
+              if ((mixed >> c4) & 1u) mask_chunk(v, lim - 32 * c4);
+#pragma unroll
+              for (int k = 0; k < 16; ++k) {
+                float y0, y1;
+                unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(v[2 * k]), __uint_as_float(v[2 * k + 1])), scale2, nmref2),
+                             y0, y1);
+                const float p0 = fast_exp2(y0), p1 = fast_exp2(y1);
+                ls2[k & 3] = add_f32x2(ls2[k & 3], pack_f32x2(p0, p1));
+                pk[k] = pack16(p0, p1, p.is_bf16);
+              }
             } else {
-              zero16(tp + cA * 16);
-              if (cB < nv_b) tmem_ld32(tb + cB * 32, a1);
+#pragma unroll
+              for (int k = 0; k < 16; ++k) pk[k] = 0u;
             }
-            if (cB < nv_b) {
-              tc_wait_ld();
-              if (c2 == 0 && 1 < nv_b) tmem_ld32(tb + 32, a0);
-              if ((mixed_b >> cB) & 1u) mask_chunk(a1, lim_b - 32 * cB);
-              exp32(a1, tp + cB * 16);
-            } else {
-              zero16(tp + cB * 16);
-              if (c2 == 0 && 1 < nv_b) tmem_ld32(tb + 32, a0);
-            }
+            tmem_st16(tP + c4 * 16, pk);
           }
         }
         float l;
@@ -454,14 +442,23 @@ block_sparse_attn_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __g
           unpack_f32x2(add_f32x2(add_f32x2(ls2[0], ls2[1]), add_f32x2(ls2[2], ls2[3])), l0, l1);
           l = l0 + l1;
         }
+        if (blk == 0) {
+          // block a's row sum travels to the output warpgroup in this warpgroup's exchange slot, once both
+          // warpgroups have read the maxima out of the slots
+          if (!__all_sync(0xffffffffu, mbar_wait(sbar(s, XCH2), rc & 1, abort_flag))) { ok = false; break; }
+          *x_a = l;
+        }
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(sbar(s, P_READY));
         if (lane == 0) XB_TRACE_EV(0x33, rc);
-        // ---- output: O / l from columns [64, 192) of the stream
+        if (blk == 0) continue;                        // the warpgroup of block a goes on to the next head's scores
+        // ---- output (warpgroup of block b): O / l from columns [64, 192) of the stream
         if (!__all_sync(0xffffffffu, mbar_wait(sbar(s, O_FULL), rc & 1, abort_flag))) { ok = false; break; }
         tc_fence_after();
         if (lane == 0) XB_TRACE_EV(0x42, rc);
+        l += *x_a;                                     // (read before the tensor memory is handed back: the other
+                                                       // warpgroup reuses the slot in the next round)
         const float inv = l > 0.f ? 1.f / l : 0.f;
         const int q_row0 = qb * 128 + quad * 32;
         auto load_half = [&](int half, uint4 (&pk)[8]) {   // O columns [64 half, 64 half + 64), normalised, 16 bit
@@ -502,16 +499,13 @@ block_sparse_attn_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __g
         {
           uint4 pk0[8];
           load_half(0, pk0);
-          {
-            uint4 pk1[8];
-            load_half(1, pk1);
-            // the stream's tensor memory is free for the next head's Q.K^T as soon as O has left it
-            tc_fence_before();
-            mbar_arrive(sbar(s, TMEM_FREE));
-            if (lane == 0) XB_TRACE_EV(0x43, rc);
-            stage_and_store(pk1, 1);
-          }
           stage_and_store(pk0, 0);
+          load_half(1, pk0);
+          // the stream's tensor memory is free for the next head's Q.K^T as soon as O has left it
+          tc_fence_before();
+          mbar_arrive(sbar(s, TMEM_FREE));
+          if (lane == 0) XB_TRACE_EV(0x43, rc);
+          stage_and_store(pk0, 1);
         }
         if (lane == 0) XB_TRACE_EV(0x44, rc);
       }
@@ -528,7 +522,7 @@ block_sparse_attn_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __g
     if (threadIdx.x == 0 && status) atomicExch(status, static_cast<int>(kDevWaitTimeout));
     __syncthreads();
   }
-  if (warp == 9) {
+  if (warp == 17) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
@@ -547,12 +541,14 @@ bool pair_path_applies(int hq, int hkv, int k_len) {
 }
 
 // Classifies the group items, runs the pair kernel on those that qualify and leaves in *cnt_rest the block counts
-// the general kernel has to honour (-1: already computed here).  The workspace is laid out as
-// [counter, padding to 256 B][PairEntry x group items][int32 x items].
+// the general kernel has to honour (-1: already computed here) provided pair_path_chosen(*header) holds on the
+// device; otherwise the pair kernel has done nothing.  The workspace is laid out as
+// [header, padding to 256 B][PairEntry x group items][int32 x items].
+
 int block_sparse_attn_pair_launch(const CUtensorMap& tmQ, const CUtensorMap& tmKf, const CUtensorMap& tmVf,
                                   const AttnParams& p, const int32_t* block_idx, const int32_t* block_cnt, void* out,
-                                  void* workspace, size_t workspace_bytes, const int32_t** cnt_rest, int* status,
-                                  cudaStream_t stream) {
+                                  void* workspace, size_t workspace_bytes, const int32_t** cnt_rest,
+                                  const int** header, int min_share_pct, int* status, cudaStream_t stream) {
   if (workspace_bytes < pair_workspace_bytes(p.batch, p.hq, p.hkv, p.q_len)) return XATTN_B200_ERR_WORKSPACE;
   if ((reinterpret_cast<uintptr_t>(workspace) & 15) != 0) return XATTN_B200_ERR_ARG;
   const long long units_ll = static_cast<long long>(p.batch) * p.hkv * p.q_blocks;
@@ -566,7 +562,7 @@ int block_sparse_attn_pair_launch(const CUtensorMap& tmQ, const CUtensorMap& tmK
   CUtensorMap tmO;
   int rc;
   if ((rc = make_qkv_map(&tmO, out, p.q_len, p.hq, p.batch, p.osb, p.osh, p.osl, 32, 1))) return rc;
-  if (cudaMemsetAsync(counter, 0, 16, stream) != cudaSuccess) return XATTN_B200_ERR_CUDA;
+  if (cudaMemsetAsync(counter, 0, 32, stream) != cudaSuccess) return XATTN_B200_ERR_CUDA;
   pair_classify_kernel<<<(units + 255) / 256, 256, 0, stream>>>(block_idx, block_cnt, p.batch, p.hq, p.hkv, p.q_blocks,
                                                                p.list_k_blocks, list, counter, rest);
   if ((rc = launch_status())) return rc;
@@ -578,11 +574,13 @@ int block_sparse_attn_pair_launch(const CUtensorMap& tmQ, const CUtensorMap& tmK
   // the number of qualifying items is known on the device only: launch for the worst case, a launch whose share
   // of the list is empty ends at once
   for (long long off = 0; off < units; off += static_cast<long long>(grid) * kPairSchedCap) {
-    block_sparse_attn_pair_kernel<<<grid, kPairThreads, kPairSmem, stream>>>(tmQ, tmKf, tmVf, tmO, p, list, counter,
-                                                                            static_cast<int>(off), out, status);
-    if ((rc = launch_status())) return rc;
+    if ((rc = launch_dependent(block_sparse_attn_pair_kernel, dim3(grid), dim3(kPairThreads), kPairSmem, stream, tmQ,
+                               tmKf, tmVf, tmO, p, static_cast<const PairEntry*>(list),
+                               static_cast<const int*>(counter), static_cast<int>(off), min_share_pct, out, status)))
+      return rc;
   }
   *cnt_rest = rest;
+  *header = counter;
   return XATTN_B200_OK;
 }
 

@@ -6,6 +6,7 @@
 #include <stdint.h>
 
 #include <atomic>
+#include <utility>
 
 #include "../../../include/xattn_b200.h"
 
@@ -78,6 +79,26 @@ inline std::atomic<unsigned long long>& launch_counter() {
 inline int launch_status() {
   launch_counter().fetch_add(1, std::memory_order_relaxed);
   return cudaGetLastError() == cudaSuccess ? XATTN_B200_OK : XATTN_B200_ERR_CUDA;
+}
+
+// Launches `kernel` so that it may start while the kernel before it in the stream is still running (programmatic
+// stream serialization): the kernel must execute pdl_wait() before it touches anything that kernel writes.
+template <typename... KArgs, typename... Args>
+inline int launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem_bytes, cudaStream_t stream,
+                            Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem_bytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+  launch_counter().fetch_add(1, std::memory_order_relaxed);
+  return (e == cudaSuccess && cudaGetLastError() == cudaSuccess) ? XATTN_B200_OK : XATTN_B200_ERR_CUDA;
 }
 
 }  // namespace xb

@@ -115,6 +115,14 @@ __device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity, vo
   }
 }
 
+// ------------------------------------------------------------------ programmatic dependent launch
+// A kernel launched with the programmatic-stream-serialization attribute may start once every CTA of the kernel
+// before it in the stream has executed pdl_launch_dependents() or exited; what that kernel wrote is visible only
+// after pdl_wait(), which returns when it has completed as a whole.  In a kernel launched without the attribute
+// both are no-ops.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ------------------------------------------------------------------ TMA
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
