@@ -42,11 +42,12 @@ import torch  # noqa: E402
 
 METRIC = "prefill_attention_effective_tflops"
 UNIT = "TFLOP/s (dense-equivalent, 4*Lq*Lk*D*Hq/2 causal)"
-# dram__bytes_read.sum + dram__bytes_write.sum of ONE block_sparse_attn_kernel launch, from ncu captures of this
-# benchmark's own command line.  32K: the full workload (405.4 MB read + 234.1 MB written).  128K: captured on two
-# of the eight kv-head groups (--heads-limit 2: 404.4 MB + 231.5 MB) and multiplied by four -- every (kv group)
-# reads and writes its own Q, K, V and O, so the traffic grows in proportion.
-NCU_ATTENTION_TRAFFIC_BYTES = {"llama3_8b_32k": 639_545_088, "llama3_8b_128k": 4 * 635_952_896}
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the attention kernel that does the bulk of the call,
+# from ncu captures of this benchmark's own command line.  32K: block_sparse_attn_kernel on the full workload
+# (405.4 MB read + 234.1 MB written).  128K: block_sparse_attn_pair_kernel, captured on two of the eight kv-head
+# groups (--heads-limit 2: 421.3 MB + 219.8 MB) and multiplied by four -- every kv group reads and writes its own
+# Q, K, V and O, so the traffic grows in proportion.
+NCU_ATTENTION_TRAFFIC_BYTES = {"llama3_8b_32k": 639_545_088, "llama3_8b_128k": 4 * 641_088_000}
 DEFAULT_WORKLOAD = "llama3_8b_32k"
 LONG_WORKLOAD = "llama3_8b_128k"
 

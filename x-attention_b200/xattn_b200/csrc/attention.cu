@@ -45,7 +45,6 @@ constexpr int kStageBytes = 4 * 32 * 128;                     // per epilogue wa
 constexpr int kAttnSmem = kAttnSmemTiles + 2 * 2 * 128 * 4 /*row sums*/ + 512 /*barriers*/ +
                           3 * kSchedCap * 2 /*schedule*/ + 16 + kStageBytes;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
-constexpr uint16_t kSkipItem = 0xFFFFu;    // schedule entry of an item another kernel computes (see block_sparse_attn_launch)
 
 // Register budget of a role.  The kernel is launched with 512 threads x 128 registers; setmaxnreg moves registers
 // between warpgroups inside that allocation (8 x softmax + 4 x epilogue + 4 x load/MMA warps = 2048 per lane).
@@ -64,6 +63,7 @@ struct Item {
 };
 __device__ __forceinline__ Item decode_item(const AttnParams& p, int t) {
   Item it;
+  if (p.item_list) t = __ldg(p.item_list + t);
   it.h = t % p.hq;
   const int rest = t / p.hq;
   it.b = rest % p.batch;
@@ -754,7 +754,6 @@ __device__ __forceinline__ void attn_cta(const CUtensorMap& tmQ, const CUtensorM
       uint8_t* orow = static_cast<uint8_t*>(out) +
                       2 * (static_cast<int64_t>(it.b) * p.osb + static_cast<int64_t>(it.h) * p.osh +
                            static_cast<int64_t>(store ? q_pos : 0) * p.osl);
-      if (n == kSkipItem) continue;
       if (n == 0) {
         if (store) {
           uint4* dst = reinterpret_cast<uint4*>(orow);
@@ -857,16 +856,20 @@ __device__ __forceinline__ void attn_cta(const CUtensorMap& tmQ, const CUtensorM
 __global__ void __launch_bounds__(kAttnThreads, 1)
 block_sparse_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                          const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmKf,
-                         const __grid_constant__ CUtensorMap tmVf, const AttnParams p,
+                         const __grid_constant__ CUtensorMap tmVf, const AttnParams p_in,
                          const int32_t* __restrict__ block_idx, const int32_t* __restrict__ block_cnt,
-                         const int32_t* __restrict__ cnt_rest, const int* __restrict__ pair_header,
+                         const int32_t* __restrict__ rest_list, const int* __restrict__ pair_header,
                          int pair_min_share, void* __restrict__ out, int* status) {
   extern __shared__ __align__(1024) uint8_t smem[];
-  // with a pair kernel in front: its leftovers if it ran, the original counts if it declined.  In that case this
-  // kernel was launched while the pair kernel was running and first waits for it (and so for the classify kernel
-  // before it) to end.
+  // with a pair kernel in front: the items it left (a list, spread evenly over the CTAs) if it ran, all items if it
+  // declined.  In that case this kernel was launched while the pair kernel was running and first waits for it (and
+  // so for the classify kernel before it) to end.
   pdl_wait();
-  if (cnt_rest && pair_path_chosen(pair_header, pair_min_share)) block_cnt = cnt_rest;
+  AttnParams p = p_in;
+  if (rest_list && pair_path_chosen(pair_header, pair_min_share)) {
+    p.item_list = rest_list;
+    p.total_items = *reinterpret_cast<const volatile int*>(pair_header + kPairRestCount);
+  }
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   if ((smem_u32(smem) & 1023u) != 0) {              // the swizzled tiles need 1024-byte alignment
@@ -880,16 +883,15 @@ block_sparse_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
   const int G = gridDim.x;
   const int n_local = (p.total_items - static_cast<int>(blockIdx.x) + G - 1) / G;     // host guarantees <= kSchedCap
   for (int i = threadIdx.x; i < n_local; i += kAttnThreads) {
-    // a negative count marks an item that the pair kernel has computed already: no work and no output here
     const int c = __ldg(block_cnt + decode_item(p, blockIdx.x + i * G).row);
-    sch_cnt[i] = c < 0 ? kSkipItem : static_cast<uint16_t>(c > 65534 ? 65534 : c);
+    sch_cnt[i] = static_cast<uint16_t>(c > 65534 ? 65534 : c);
   }
   __syncthreads();
   if (warp == 0) {
     int running = 0, blocks = 0;
     for (int base = 0; base < n_local; base += 32) {
       const int i = base + lane;
-      const int c = (i < n_local && sch_cnt[i] != kSkipItem) ? sch_cnt[i] : 0;
+      const int c = i < n_local ? sch_cnt[i] : 0;
       const bool ne = c > 0;
       const unsigned bal = __ballot_sync(0xffffffffu, ne);
       const int k = running + __popc(bal & ((1u << lane) - 1u));
@@ -915,7 +917,7 @@ size_t pair_workspace_bytes(int batch, int hq, int hkv, int q_len);
 bool pair_path_applies(int hq, int hkv, int k_len);
 int block_sparse_attn_pair_launch(const CUtensorMap& tmQ, const CUtensorMap& tmKf, const CUtensorMap& tmVf,
                                   const AttnParams& p, const int32_t* block_idx, const int32_t* block_cnt, void* out,
-                                  void* workspace, size_t workspace_bytes, const int32_t** cnt_rest,
+                                  void* workspace, size_t workspace_bytes, const int32_t** rest_list,
                                   const int** header, int min_share_pct, int* status, cudaStream_t stream);
 
 // Share (per cent) of a call's listed blocks that must qualify for the pair kernel before the call is split; a
@@ -961,6 +963,7 @@ int block_sparse_attn_launch(const void* q, const void* k, const void* v, int dt
   p.causal = causal ? 1 : 0; p.is_bf16 = dtype == XATTN_B200_BF16 ? 1 : 0;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.osb = osb; p.osh = osh; p.osl = osl;
+  p.item_list = nullptr;
   if (cudaFuncSetAttribute(block_sparse_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem) !=
       cudaSuccess)
     return XATTN_B200_ERR_CUDA;

@@ -18,6 +18,7 @@ struct AttnParams {
   int total_items;
   float scale_log2;
   int64_t osb, osh, osl;
+  const int32_t* item_list;     // general kernel: its work items (null: all of them, 0 .. total_items - 1)
 };
 
 __device__ __forceinline__ uint32_t pack16(float lo, float hi, int is_bf16) {
@@ -69,16 +70,16 @@ static inline int make_qkv_map(CUtensorMap* m, const void* base, int len, int he
 
 
 // ---------------------------------------------------------------- split between the pair and the general kernel
-// Workspace header, in 32-bit words: [0] length of the pair list, [2..3] / [4..5] 64-bit totals of the blocks listed
-// by all items / by the items on the pair list.
-constexpr int kPairTotalAll = 2, kPairTotalTaken = 4;
+// Workspace header, in 32-bit words: [0] length of the pair list, [1] length of the list of items left to the
+// general kernel, [2..3] / [4..5] 64-bit totals of the blocks listed by all items / by the items on the pair list.
+constexpr int kPairRestCount = 1, kPairTotalAll = 2, kPairTotalTaken = 4;
 constexpr int kPairMinSharePct = 92;
 
 // The split into two kernels costs a second kernel tail, so it pays only when nearly all the work goes to the pair
 // kernel: measured on Llama-3.1-8B shapes, 95 % of the blocks on the pair list made the call 8 % faster, 89 % left
 // it unchanged and 66 % made it 11 % slower.  Both kernels evaluate this after the classify kernel has finished
 // and so agree: below the mark (kPairMinSharePct unless the caller set another, see pair_min_share_pct) the pair
-// kernel returns at once and the general kernel reads the original counts.
+// kernel returns at once and the general kernel computes every item.
 __device__ __forceinline__ bool pair_path_chosen(const int* header, int min_share_pct) {
   const unsigned long long all = *reinterpret_cast<const volatile unsigned long long*>(header + kPairTotalAll);
   const unsigned long long taken = *reinterpret_cast<const volatile unsigned long long*>(header + kPairTotalTaken);

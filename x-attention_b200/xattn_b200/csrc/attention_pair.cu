@@ -56,12 +56,13 @@ struct PairEntry {
 
 // ------------------------------------------------------------------------------------------------ classify
 // One thread per group item: it qualifies when every query head of the group lists the same one or two blocks.
-// Qualifying items go to `list` (order: as the atomics fall; every item is computed independently, so the
-// order changes nothing in the result) and are marked -1 in `cnt_rest`; all other items keep their count there.
+// Qualifying items go to `list`, the work items (batch, query head, query block) of all others to `rest_list` in
+// the general kernel's numbering (order: as the atomics fall; every item is computed independently, so the order
+// changes nothing in the result).  The general kernel then takes its items from that list, evenly over its CTAs.
 __global__ void pair_classify_kernel(const int32_t* __restrict__ block_idx, const int32_t* __restrict__ block_cnt,
                                      int batch, int hq, int hkv, int q_blocks, int list_k_blocks,
                                      PairEntry* __restrict__ list, int* __restrict__ counter,
-                                     int32_t* __restrict__ cnt_rest) {
+                                     int32_t* __restrict__ rest_list) {
   pdl_launch_dependents();          // the pair kernel's CTAs may take their places; they wait for this grid to end
   const int units = batch * hkv * q_blocks;
   const int u = blockIdx.x * blockDim.x + threadIdx.x;
@@ -89,13 +90,14 @@ __global__ void pair_classify_kernel(const int32_t* __restrict__ block_idx, cons
       list[pos].unit = u;
       list[pos].blocks = static_cast<uint32_t>(i0) | ((c0 == 2 ? static_cast<uint32_t>(i1) : kNoBlock) << 16);
     }
-    for (int j = 0; j < group; ++j) {
-      const size_t row = row0 + static_cast<size_t>(j) * q_blocks;
-      const int c = __ldg(block_cnt + row);
-      cnt_rest[row] = ok ? -1 : c;
-      total += c;
-    }
+    for (int j = 0; j < group; ++j) total += __ldg(block_cnt + row0 + static_cast<size_t>(j) * q_blocks);
     taken = ok ? total : 0;
+    if (!ok) {
+      // work item t of the general kernel: t = ((q_blocks - 1 - qb) * batch + b) * hq + h
+      const int pos = atomicAdd(counter + kPairRestCount, group);
+      const int t0 = ((q_blocks - 1 - qb) * batch + b) * hq + g * group;
+      for (int j = 0; j < group; ++j) rest_list[pos + j] = t0 + j;
+    }
   }
   // block totals for pair_path_chosen(): one atomic per warp and word
 #pragma unroll
@@ -540,14 +542,14 @@ bool pair_path_applies(int hq, int hkv, int k_len) {
   return group >= 2 && group % 2 == 0 && (k_len + 127) / 128 < static_cast<int>(kNoBlock);
 }
 
-// Classifies the group items, runs the pair kernel on those that qualify and leaves in *cnt_rest the block counts
-// the general kernel has to honour (-1: already computed here) provided pair_path_chosen(*header) holds on the
+// Classifies the group items, runs the pair kernel on those that qualify and leaves in *rest_list the work items
+// the general kernel has to compute (their number in the header) provided pair_path_chosen(*header) holds on the
 // device; otherwise the pair kernel has done nothing.  The workspace is laid out as
 // [header, padding to 256 B][PairEntry x group items][int32 x items].
 
 int block_sparse_attn_pair_launch(const CUtensorMap& tmQ, const CUtensorMap& tmKf, const CUtensorMap& tmVf,
                                   const AttnParams& p, const int32_t* block_idx, const int32_t* block_cnt, void* out,
-                                  void* workspace, size_t workspace_bytes, const int32_t** cnt_rest,
+                                  void* workspace, size_t workspace_bytes, const int32_t** rest_list,
                                   const int** header, int min_share_pct, int* status, cudaStream_t stream) {
   if (workspace_bytes < pair_workspace_bytes(p.batch, p.hq, p.hkv, p.q_len)) return XATTN_B200_ERR_WORKSPACE;
   if ((reinterpret_cast<uintptr_t>(workspace) & 15) != 0) return XATTN_B200_ERR_ARG;
@@ -579,7 +581,7 @@ int block_sparse_attn_pair_launch(const CUtensorMap& tmQ, const CUtensorMap& tmK
                                static_cast<const int*>(counter), static_cast<int>(off), min_share_pct, out, status)))
       return rc;
   }
-  *cnt_rest = rest;
+  *rest_list = rest;
   *header = counter;
   return XATTN_B200_OK;
 }
