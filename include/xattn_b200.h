@@ -244,9 +244,12 @@ int xattn_b200_block_sparse_attn(const void* q, const void* k, const void* v, in
  * xattn_b200_block_sparse_attn_split_share(percent) replaces the 92 for the calls enqueued after it (0: split
  * whenever anything qualifies, 101: never) and returns the previous value; a negative argument only reads it.
  * Same call-site contract (xattn/src/Xattention.py:377-391), same results up to the summation order.
+ * A non-causal call uses the scratch memory differently: its work items (batch, query head, query block) are sorted
+ * by list length, longest first, by one small kernel, and dealt to the SMs in that order; masks whose rows differ
+ * widely in length (video diffusion: 5 to 891 blocks per row) otherwise leave the most loaded SM 16 % above the mean.
  * workspace: device memory of xattn_b200_block_sparse_attn_workspace_bytes() bytes, 16-byte aligned, contents
- * irrelevant on entry; the call's kernels use it until they finish.  A size of 0 means the shape gains nothing
- * (hq / hkv odd or 1) and the call equals xattn_b200_block_sparse_attn; NULL is then accepted.
+ * irrelevant on entry; the call's kernels use it until they finish.  With workspace == NULL the call equals
+ * xattn_b200_block_sparse_attn.
  */
 size_t xattn_b200_block_sparse_attn_workspace_bytes(int batch, int hq, int hkv, int q_len, int k_len);
 int xattn_b200_block_sparse_attn_split_share(int percent);

@@ -289,15 +289,45 @@ def test_short_shared_lists_take_the_pair_kernel(causal, dtype, hq, hkv, lq, lk)
     try:
         n0 = ops._lib.load().xattn_b200_launch_count()
         out = ops.block_sparse_attention(q.to(DEV), k.to(DEV), v.to(DEV), idx, cnt, causal,
-                                         use_pair_kernel=True).float().cpu()
-        assert ops._lib.load().xattn_b200_launch_count() - n0 == 3      # classify, pair kernel, general kernel
+                                         use_workspace=True).float().cpu()
+        # causal: classify, pair kernel, general kernel; non-causal calls sort their items instead: order, general
+        assert ops._lib.load().xattn_b200_launch_count() - n0 == (3 if causal else 2)
     finally:
         ops.pair_split_share(before)
     ref = orc.block_sparse_attention_oracle(q, k, v, mask, causal)
     err = (out - ref).abs()
     assert err.max() < OUT_MAX_ABS and err.mean() < OUT_MEAN_ABS, (err.max(), err.mean())
-    gen = ops.block_sparse_attention(q.to(DEV), k.to(DEV), v.to(DEV), idx, cnt, causal, use_pair_kernel=False)
+    gen = ops.block_sparse_attention(q.to(DEV), k.to(DEV), v.to(DEV), idx, cnt, causal, use_workspace=False)
     _assert_same_up_to_body_choice(out, gen.float().cpu())
+
+
+@pytest.mark.parametrize("hq,hkv,L", [(4, 4, 6400), (3, 1, 2000), (6, 2, 128 * 75)])
+def test_non_causal_items_sorted_by_list_length(hq, hkv, L):
+    """With scratch memory a non-causal call deals its work items longest list first, in alternating direction over
+    the SMs (more than one row of the deal for the first and last shape, a partial last row in all).  Every row must
+    still be computed exactly once: against the oracle, and against the call without scratch memory, on a mask whose
+    rows list between one block and all of them; the output buffer starts as NaN."""
+    from xattn_b200 import ops
+    g = torch.Generator().manual_seed(L + hq)
+    q = torch.randn(1, hq, L, 128, generator=g).bfloat16()
+    k = torch.randn(1, hkv, L, 128, generator=g).bfloat16()
+    v = torch.randn(1, hkv, L, 128, generator=g).bfloat16()
+    nb = (L + 127) // 128
+    want = (torch.rand(1, hq, nb, 1, generator=g) ** 3 * nb).long().clamp(1, nb)       # skewed list lengths
+    mask = torch.rand(1, hq, nb, nb, generator=g).argsort(-1).argsort(-1) < want
+    mask[0, 0, 0, :] = True                                                            # one row lists every block
+    mask[0, hq - 1, nb - 1, :] = False                                                 # and one lists none
+    idx, cnt = ops.mask_to_lists(mask.to(DEV), L, L, False)
+    outs = []
+    for ws in (True, False):
+        buf = torch.full((1, L, hq, 128), float("nan"), dtype=torch.bfloat16, device=DEV).transpose(1, 2)
+        ops.block_sparse_attention(q.to(DEV), k.to(DEV), v.to(DEV), idx, cnt, False, out=buf, use_workspace=ws)
+        outs.append(buf.float().cpu())
+    assert not torch.isnan(outs[0]).any()
+    ref = orc.block_sparse_attention_oracle(q, k, v, mask, False)
+    err = (outs[0] - ref).abs()
+    assert err.max() < OUT_MAX_ABS and err.mean() < OUT_MEAN_ABS, (err.max(), err.mean())
+    _assert_same_up_to_body_choice(outs[0], outs[1])
 
 
 def test_pair_kernel_is_declined_on_the_device_when_few_blocks_qualify():
@@ -318,8 +348,8 @@ def test_pair_kernel_is_declined_on_the_device_when_few_blocks_qualify():
     for base, split in ((three, False), (two, True)):
         mask = base[None, None].expand(1, hq, -1, -1).contiguous()
         idx, cnt = ops.mask_to_lists(mask.to(DEV), L, L, True)
-        gen = ops.block_sparse_attention(q, k, v, idx, cnt, True, use_pair_kernel=False).clone()
-        both = ops.block_sparse_attention(q, k, v, idx, cnt, True, use_pair_kernel=True)
+        gen = ops.block_sparse_attention(q, k, v, idx, cnt, True, use_workspace=False).clone()
+        both = ops.block_sparse_attention(q, k, v, idx, cnt, True, use_workspace=True)
         if split:
             assert not torch.equal(both, gen)                      # another summation order: the pair kernel ran
             _assert_same_up_to_body_choice(both.float().cpu(), gen.float().cpu())

@@ -19,6 +19,7 @@ struct AttnParams {
   float scale_log2;
   int64_t osb, osh, osl;
   const int32_t* item_list;     // general kernel: its work items (null: all of them, 0 .. total_items - 1)
+  int snake;                    // general kernel: deal the items to the CTAs in alternating direction (sorted list)
 };
 
 __device__ __forceinline__ uint32_t pack16(float lo, float hi, int is_bf16) {

@@ -249,6 +249,9 @@ def mask_to_lists(mask: torch.Tensor, q_len: int, k_len: int, causal: bool):
 # once): 11 % of a Llama-3.1-8B call at 32K or 64K tokens, where the library does decline (66 % / 89 % of the blocks
 # qualify), against the 8 % it wins at 128K (95 %).  So the attempt is made by default from 96K tokens on.
 PAIR_MIN_Q_BLOCKS = 768
+# Non-causal calls: sorting the items by list length is one launch of a few microseconds; with only a few items per
+# SM there is nothing to balance.
+ORDER_MIN_ITEMS = 16 * 148
 
 
 def pair_split_share(percent: Optional[int] = None) -> int:
@@ -260,16 +263,18 @@ def pair_split_share(percent: Optional[int] = None) -> int:
 
 def block_sparse_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, block_idx: torch.Tensor,
                            block_cnt: torch.Tensor, causal: bool = True, scale: Optional[float] = None,
-                           out: Optional[torch.Tensor] = None, use_pair_kernel: Optional[bool] = None) -> torch.Tensor:
+                           out: Optional[torch.Tensor] = None, use_workspace: Optional[bool] = None) -> torch.Tensor:
     """q [B,Hq,Lq,128], k/v [B,Hkv,Lk,128] (bf16/fp16; fp32 is computed in bf16) -> [B,Hq,Lq,128], returned
     as a transposed view of [B,Lq,Hq,128] storage, like the reference's output (Xattention.py:392-394).
     `out`, if given, is a [B,Hq,Lq,128] tensor of the compute dtype (any strides, unit stride on the last
-    dimension, 16-byte aligned rows) that receives the result instead.  `use_pair_kernel=True` hands the library
-    the scratch memory with which it may send the rows whose kv group shares a list of one or two blocks to the kernel
-    that loads K/V once per group and treats both blocks in one softmax pass (xattn_b200_block_sparse_attn_ws); the
-    library takes that route only when those rows list at least `pair_split_share()` per cent of the blocks, which it
-    finds out on the device.  A declined attempt costs 30-45 us, so by default (None) it is made only for calls of
-    at least PAIR_MIN_Q_BLOCKS query blocks; False never makes it."""
+    dimension, 16-byte aligned rows) that receives the result instead.  `use_workspace=True` hands the library
+    scratch memory (xattn_b200_block_sparse_attn_ws).  Causal calls: it may then send the rows whose kv group shares a
+    list of one or two blocks to the kernel that loads K/V once per group and treats both blocks in one softmax pass;
+    the library takes that route only when those rows list at least `pair_split_share()` per cent of the blocks,
+    which it finds out on the device, and a declined attempt costs 30-45 us, so by default (None) the memory is
+    offered only to calls of at least PAIR_MIN_Q_BLOCKS query blocks.  Non-causal calls: the work items are sorted
+    by list length before they are dealt to the SMs (one small kernel); offered by default from ORDER_MIN_ITEMS
+    items on.  False: the general kernel alone, items in their natural order."""
     _require_cuda(q, k, v, block_idx, block_cnt)
     lib = _lib.load()
     B, Hq, Lq, D = q.shape
@@ -292,9 +297,9 @@ def block_sparse_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, bl
     lqb, lkb = (Lq + 127) // 128, (Lk + 127) // 128
     if tuple(block_idx.shape) != (B, Hq, lqb, lkb) or tuple(block_cnt.shape) != (B, Hq, lqb):
         raise ValueError("block lists have the wrong shape")
-    if use_pair_kernel is None:
-        use_pair_kernel = lqb >= PAIR_MIN_Q_BLOCKS
-    ws_bytes = lib.xattn_b200_block_sparse_attn_workspace_bytes(B, Hq, Hkv, Lq, Lk) if use_pair_kernel else 0
+    if use_workspace is None:
+        use_workspace = lqb >= PAIR_MIN_Q_BLOCKS if causal else B * Hq * lqb >= ORDER_MIN_ITEMS
+    ws_bytes = lib.xattn_b200_block_sparse_attn_workspace_bytes(B, Hq, Hkv, Lq, Lk) if use_workspace else 0
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device) if ws_bytes else None
     _lib.check(lib.xattn_b200_block_sparse_attn_ws(
         q.data_ptr(), k.data_ptr(), v.data_ptr(), _DT[q.dtype], B, Hq, Hkv, Lq, Lk, D,
