@@ -339,7 +339,8 @@ def attention_roofline(name, prof, peaks):
     a = prof["rooflines"]["attend"]
     from xattn_b200 import ops, synth
     w = synth.WORKLOADS[name]
-    split = w.seq_len // 128 >= ops.PAIR_MIN_Q_BLOCKS and w.hq // w.hkv >= 2 and (w.hq // w.hkv) % 2 == 0
+    split = (w.seq_len // 128 >= ops.PAIR_MIN_K_BLOCKS and w.hq * (w.seq_len // 128) >= ops.PAIR_MIN_ITEMS
+             and w.hq // w.hkv >= 2 and (w.hq // w.hkv) % 2 == 0)
     kernel = ("block_sparse_attn_pair_kernel (rows whose kv group shares a list of one or two blocks) + "
               "block_sparse_attn_kernel (the rest), one call") if split else "block_sparse_attn_kernel"
     return dict(bound=a["bound"], kernel=kernel, achieved=a["tflops"], peak=peaks["bf16"],
@@ -387,6 +388,8 @@ def measure_workload(name, args, rank, dist, device, peaks, steps, warmup, seed,
     dq, dk, dv, w = synth.make_inputs(name, seed=seed, device=device, heads_limit=args.heads_limit)
     if args.heads_limit is not None:             # a kv-group slice of the workload (small captures under a profiler)
         import dataclasses
+        # the slice stands for the whole workload: it takes the attention kernels the whole workload would take
+        ops.PAIR_MIN_ITEMS = ops.PAIR_MIN_ITEMS * dk.shape[1] // w.hkv
         w = dataclasses.replace(w, hq=dq.shape[1], hkv=dk.shape[1], name=f"{w.name}[{dk.shape[1]} kv group(s)]")
     chunk = w.chunk_size or ops.default_chunk_size(w.seq_len)
     q_pin, k_pin, v_pin = dq.cpu().pin_memory(), dk.cpu().pin_memory(), dv.cpu().pin_memory()

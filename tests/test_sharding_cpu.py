@@ -156,15 +156,18 @@ def test_host_pipeline_steps_keep_the_kv_head_mapping():
     for hq, hkv in ((32, 8), (12, 3), (28, 4), (24, 24), (8, 1), (6, 2)):
         rep = hq // hkv
         for gps in (1, 2, 3):
-            for splits in (0, 1, 2, 4):
-                steps = plan_steps(hq, hkv, gps, splits)
+            for splits, tail in ((0, 1), (1, 1), (2, 1), (4, 1), (1, 2), (1, 4), (2, 4)):
+                steps = plan_steps(hq, hkv, gps, splits, tail)
+                if tail > 1 and gps == 1 and rep % tail == 0:
+                    # only the last slice is cut finer than the others
+                    assert sum(1 for st in steps if st[2] == hkv - 1) == max(tail, splits if rep % max(splits, 1) == 0 else 1)
                 seen = []
                 firsts = 0
                 for (q0, q1, k0, k1, first, last) in steps:
                     nq, nk = q1 - q0, k1 - k0
                     assert nq > 0 and nk > 0 and nq % nk == 0
                     for h in range(nq):
-                        assert k0 + h // (nq // nk) == (q0 + h) // rep, (hq, hkv, gps, splits, q0, h)
+                        assert k0 + h // (nq // nk) == (q0 + h) // rep, (hq, hkv, gps, splits, tail, q0, h)
                     seen.extend(range(q0, q1))
                     firsts += int(first)
                 assert seen == list(range(hq))

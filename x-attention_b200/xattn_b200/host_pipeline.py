@@ -62,15 +62,19 @@ def group_slices(hq: int, hkv: int, groups_per_step: int = 1):
     return out
 
 
-def plan_steps(hq: int, hkv: int, groups_per_step: int = 1, q_splits: int = 1):
+def plan_steps(hq: int, hkv: int, groups_per_step: int = 1, q_splits: int = 1, tail_splits: int = 1):
     """Steps of the host pipeline: [(q0, q1, k0, k1, first_of_slice, last_of_slice)].  A slice is `groups_per_step`
     whole kv groups (its K/V are copied with its first step); the query heads of a slice that holds ONE kv head
-    run in `q_splits` steps when that divides them.  A slice with several kv heads is never split: the kernels
-    map local query head h to local kv head h // (query heads / kv heads), which a partial slice would break."""
+    run in `q_splits` steps when that divides them, those of the LAST slice in `tail_splits` steps (what follows
+    the last input copy -- the last step's kernels and its output copy -- overlaps with nothing, so that step
+    should be small).  A slice with several kv heads is never split: the kernels map local query head h to local
+    kv head h // (query heads / kv heads), which a partial slice would break."""
     steps = []
-    for (q0, q1, k0, k1) in group_slices(hq, hkv, groups_per_step):
+    slices = group_slices(hq, hkv, groups_per_step)
+    for si, (q0, q1, k0, k1) in enumerate(slices):
         n = q1 - q0
-        parts = q_splits if (q_splits > 0 and k1 - k0 == 1 and n % q_splits == 0) else 1
+        want = max(q_splits, tail_splits) if si == len(slices) - 1 else q_splits
+        parts = want if (want > 0 and k1 - k0 == 1 and n % want == 0) else 1
         for j in range(parts):
             steps.append((q0 + j * (n // parts), q0 + (j + 1) * (n // parts), k0, k1, j == 0, j == parts - 1))
     return steps
@@ -80,13 +84,13 @@ def Xattention_prefill_host(query_states: torch.Tensor, key_states: torch.Tensor
                             stride, norm=1, threshold: Union[float, torch.Tensor] = 0.8, block_size=128,
                             causal=True, chunk_size=None, keep_sink=False, keep_recent=False,
                             device: Optional[torch.device] = None, out: Optional[torch.Tensor] = None,
-                            groups_per_step: int = 1, q_splits: int = 1) -> torch.Tensor:
+                            groups_per_step: int = 1, q_splits: int = 1, tail_splits: int = 4) -> torch.Tensor:
     """Same computation as Xattention_prefill (xattn/src/Xattention.py:302-402) for host tensors.
 
     query_states [1,Hq,L,D], key/value_states [1,Hkv,L,D] on the CPU (pin them: pageable memory makes the
     copies synchronous).  Returns a pinned CPU tensor [1,Hq,L,D] (contiguous), or fills `out`.  The call
     returns when the result is complete.  `groups_per_step` kv groups are resident at a time; the query heads of
-    a group slice run in `q_splits` steps (when that divides them)."""
+    a group slice run in `q_splits` steps, those of the last slice in `tail_splits` steps (when that divides them)."""
     assert block_size == 128
     B, Hq, Lq, D = query_states.shape
     assert B == 1
@@ -101,69 +105,89 @@ def Xattention_prefill_host(query_states: torch.Tensor, key_states: torch.Tensor
         out = torch.empty(1, Hq, Lq, D, dtype=cdtype).pin_memory()
     g = ops.geometry(Lq, Lk, chunk_size, stride, block_size)
     band = ops.band_applies(Lk, chunk_size, bool(causal))
-    slices = group_slices(Hq, Hkv, groups_per_step)
-    nk = slices[0][3] - slices[0][2]
     # smaller steps shorten what cannot overlap (the first step's input copy, the last step's output copy) but make
     # more, shorter copies: on a PCIe 5 x16 link one kv group per step measured best (8.93 ms at 32K; two steps per
-    # group 9.06, four 9.76, two groups per step 9.4)
-    steps = plan_steps(Hq, Hkv, groups_per_step, q_splits)
-    nq = max(st[1] - st[0] for st in steps)
+    # group 9.06, four 9.76, two groups per step 9.4); cutting only the last group into four takes its output copy
+    # from 0.65 to 0.21 ms (8.77 ms; 128K tokens: 34.3 -> 33.4 ms).  The input copies themselves take 8.2-8.5 ms with
+    # the output copies running beside them, against 7.26 ms alone.
+    steps = plan_steps(Hq, Hkv, groups_per_step, q_splits, tail_splits)
+    slices = []                                          # [(q0, q1, k0, k1, [steps of the slice])]
+    for st in steps:
+        if st[4]:
+            slices.append([st[0], st[1], st[2], st[3], []])
+        slices[-1][1] = st[1]
+        slices[-1][4].append(st)
+    nq = max(sl[1] - sl[0] for sl in slices)
+    nk = max(sl[3] - sl[2] for sl in slices)
+    parts = max(len(sl[4]) for sl in slices)
     with torch.cuda.device(dev):
         h2d, d2h = _streams(dev)
         compute = torch.cuda.current_stream(dev)
-        qo, kv = [], []
+        # two buffer sets, one per slice in flight; a slice's steps work on sub-views of its set
+        sets = []
         for _ in range(2):
-            qo.append(dict(
+            sets.append(dict(
                 q=torch.empty(1, nq, Lq, D, dtype=query_states.dtype, device=dev),
                 o=torch.empty(1, nq, Lq, D, dtype=cdtype, device=dev),
-                loaded=torch.cuda.Event(), computed=torch.cuda.Event(), stored=torch.cuda.Event(), used=False))
-            kv.append(dict(
                 k=torch.empty(1, nk, Lk, D, dtype=key_states.dtype, device=dev),
                 v=torch.empty(1, nk, Lk, D, dtype=value_states.dtype, device=dev),
-                loaded_k=torch.cuda.Event(), loaded_v=torch.cuda.Event(), released=torch.cuda.Event(), used=False))
+                loaded_q=[torch.cuda.Event() for _ in range(parts)],
+                loaded_k=torch.cuda.Event(), loaded_v=torch.cuda.Event(),
+                released=torch.cuda.Event(),             # the slice's last kernel has run: q, k, v may be overwritten
+                stored=torch.cuda.Event(),               # the slice's last output copy has left: o may be overwritten
+                used=False))
         h2d.wait_stream(compute)
-        group_no = -1
-        for i, (q0, q1, k0, k1, first, last) in enumerate(steps):
-            if first:
-                group_no += 1
-            b, c = qo[i & 1], kv[group_no & 1]
-            hq_n, hk_n = q1 - q0, k1 - k0
+
+        def enqueue_inputs(si):
+            """All input copies of slice si, in the order the kernels need them: K, the query heads step by step,
+            V (not needed by the estimate).  Enqueued one slice ahead of the kernels, so that the copy engine never
+            waits for the host thread, however small the steps."""
+            q0s, _, k0, k1, sl_steps = slices[si]
+            c = sets[si & 1]
             with torch.cuda.stream(h2d):
-                if b["used"]:
-                    h2d.wait_event(b["computed"])          # q of step i-2 no longer needed
-                b["q"][:, :hq_n].copy_(query_states[:, q0:q1], non_blocking=True)
-                if first:
-                    if c["used"]:
-                        h2d.wait_event(c["released"])      # K/V of the group two back no longer needed
-                    c["k"][:, :hk_n].copy_(key_states[:, k0:k1], non_blocking=True)
-                    c["loaded_k"].record(h2d)
-                    b["loaded"].record(h2d)
-                    c["v"][:, :hk_n].copy_(value_states[:, k0:k1], non_blocking=True)   # not needed by the estimate
-                    c["loaded_v"].record(h2d)
-                else:
-                    b["loaded"].record(h2d)
-            compute.wait_event(b["loaded"])
+                if c["used"]:
+                    h2d.wait_event(c["released"])
+                c["k"][:, :k1 - k0].copy_(key_states[:, k0:k1], non_blocking=True)
+                c["loaded_k"].record(h2d)
+                for j, (q0, q1, *_rest) in enumerate(sl_steps):
+                    c["q"][:, q0 - q0s:q1 - q0s].copy_(query_states[:, q0:q1], non_blocking=True)
+                    c["loaded_q"][j].record(h2d)
+                    if j == 0:
+                        c["v"][:, :k1 - k0].copy_(value_states[:, k0:k1], non_blocking=True)
+                        c["loaded_v"].record(h2d)
+
+        enqueue_inputs(0)
+        for si, (q0s, _q1s, k0, k1, sl_steps) in enumerate(slices):
+            if si + 1 < len(slices):
+                enqueue_inputs(si + 1)
+            c = sets[si & 1]
+            hk_n = k1 - k0
+            kd, vd = c["k"][:, :hk_n], c["v"][:, :hk_n]
             compute.wait_event(c["loaded_k"])
-            thr = threshold[q0:q1] if isinstance(threshold, torch.Tensor) else threshold
-            qd, kd, vd = b["q"][:, :hq_n], c["k"][:, :hk_n], c["v"][:, :hk_n]
-            sums = ops.estimate_block_sums(qd, kd, stride, block_size, chunk_size, float(norm), bool(causal),
-                                           band=band)
-            _, idx, cnt = ops.select_blocks(sums, g["bpc"], g["block_offset"], thr, bool(causal), True,
-                                            bool(keep_sink), bool(keep_recent), list_shape=(Lq, Lk), want_mask=False,
-                                            band_k_blocks=g["kb"] if band else None)
-            compute.wait_event(c["loaded_v"])
-            if b["used"]:
-                compute.wait_event(b["stored"])            # output buffer of step i-2 has left the device
-            ops.block_sparse_attention(qd, kd, vd, idx, cnt, bool(causal), out=b["o"][:, :hq_n])
-            b["computed"].record(compute)
-            if last:
-                c["released"].record(compute)
-                c["used"] = True
-            with torch.cuda.stream(d2h):
-                d2h.wait_event(b["computed"])
-                out[:, q0:q1].copy_(b["o"][:, :hq_n], non_blocking=True)
-                b["stored"].record(d2h)
-            b["used"] = True
+            if c["used"]:
+                compute.wait_event(c["stored"])            # the set's output buffer (slice si - 2) has left the device
+            for j, (q0, q1, *_rest) in enumerate(sl_steps):
+                compute.wait_event(c["loaded_q"][j])
+                thr = threshold[q0:q1] if isinstance(threshold, torch.Tensor) else threshold
+                qd, od = c["q"][:, q0 - q0s:q1 - q0s], c["o"][:, q0 - q0s:q1 - q0s]
+                sums = ops.estimate_block_sums(qd, kd, stride, block_size, chunk_size, float(norm), bool(causal),
+                                               band=band)
+                _, idx, cnt = ops.select_blocks(sums, g["bpc"], g["block_offset"], thr, bool(causal), True,
+                                                bool(keep_sink), bool(keep_recent), list_shape=(Lq, Lk),
+                                                want_mask=False, band_k_blocks=g["kb"] if band else None)
+                if j == 0:
+                    compute.wait_event(c["loaded_v"])
+                ops.block_sparse_attention(qd, kd, vd, idx, cnt, bool(causal), out=od)
+                computed = torch.cuda.Event()
+                computed.record(compute)
+                if j == len(sl_steps) - 1:
+                    c["released"].record(compute)
+                with torch.cuda.stream(d2h):
+                    d2h.wait_event(computed)
+                    out[:, q0:q1].copy_(od, non_blocking=True)
+                    if j == len(sl_steps) - 1:
+                        c["stored"].record(d2h)
+            c["used"] = True
         compute.wait_stream(d2h)
         compute.wait_stream(h2d)
         compute.synchronize()

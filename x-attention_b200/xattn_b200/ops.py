@@ -245,10 +245,15 @@ def mask_to_lists(mask: torch.Tensor, q_len: int, k_len: int, causal: bool):
 
 
 # ------------------------------------------------------------------------------ phase 3
-# An attempt that the library declines costs 30-45 us (classify kernel plus a pair-kernel launch that returns at
-# once): 11 % of a Llama-3.1-8B call at 32K or 64K tokens, where the library does decline (66 % / 89 % of the blocks
-# qualify), against the 8 % it wins at 128K (95 %).  So the attempt is made by default from 96K tokens on.
-PAIR_MIN_Q_BLOCKS = 768
+# The split has fixed costs: the classify kernel (8 us) and the general kernel's pass over the rows the pair kernel
+# leaves (a few items per SM, each a full latency chain: 30-65 us), against 8-12 % of the call won when 95 % of the
+# blocks qualify (Llama-3.1-8B at 128K tokens); and an attempt that the library declines costs 30-45 us (at 32K or
+# 64K tokens it does decline: 66 % / 89 % qualify).  So the scratch memory is offered by default only for sequences
+# of at least 96K tokens (PAIR_MIN_K_BLOCKS key blocks) and calls of at least PAIR_MIN_ITEMS (batch, query head,
+# query block) items: the whole 128K-token layer (32 768 items) but not a rank's two kv heads of it (8 192 items,
+# where the general kernel alone takes 0.21 ms).
+PAIR_MIN_K_BLOCKS = 768
+PAIR_MIN_ITEMS = 24576
 # Non-causal calls: sorting the items by list length is one launch of a few microseconds; with only a few items per
 # SM there is nothing to balance.
 ORDER_MIN_ITEMS = 16 * 148
@@ -272,7 +277,7 @@ def block_sparse_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, bl
     list of one or two blocks to the kernel that loads K/V once per group and treats both blocks in one softmax pass;
     the library takes that route only when those rows list at least `pair_split_share()` per cent of the blocks,
     which it finds out on the device, and a declined attempt costs 30-45 us, so by default (None) the memory is
-    offered only to calls of at least PAIR_MIN_Q_BLOCKS query blocks.  Non-causal calls: the work items are sorted
+    offered only for sequences of at least PAIR_MIN_K_BLOCKS key blocks and calls of at least PAIR_MIN_ITEMS items.  Non-causal calls: the work items are sorted
     by list length before they are dealt to the SMs (one small kernel); offered by default from ORDER_MIN_ITEMS
     items on.  False: the general kernel alone, items in their natural order."""
     _require_cuda(q, k, v, block_idx, block_cnt)
@@ -298,7 +303,8 @@ def block_sparse_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, bl
     if tuple(block_idx.shape) != (B, Hq, lqb, lkb) or tuple(block_cnt.shape) != (B, Hq, lqb):
         raise ValueError("block lists have the wrong shape")
     if use_workspace is None:
-        use_workspace = lqb >= PAIR_MIN_Q_BLOCKS if causal else B * Hq * lqb >= ORDER_MIN_ITEMS
+        use_workspace = ((lkb >= PAIR_MIN_K_BLOCKS and B * Hq * lqb >= PAIR_MIN_ITEMS) if causal
+                         else B * Hq * lqb >= ORDER_MIN_ITEMS)
     ws_bytes = lib.xattn_b200_block_sparse_attn_workspace_bytes(B, Hq, Hkv, Lq, Lk) if use_workspace else 0
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device) if ws_bytes else None
     _lib.check(lib.xattn_b200_block_sparse_attn_ws(
