@@ -9,11 +9,13 @@
 // score/probability buffer S and output accumulator O in tensor memory and its own softmax warpgroup,
 // so the bubbles of one stream's dependency chain are filled by the other stream's work.
 //
-//   warps 0-3   softmax of stream 0  } one thread per query row.  Two passes over S in TMEM: row max
-//   warps 4-7   softmax of stream 1  } (8 independent chains), then exp2 in 32-column chunks, P packed to
-//                                      16-bit back into the S columns; lazy rescale of O only when the max
-//                                      grew by more than 2^8; the row sum of the item's last block goes to
-//                                      shared memory for the epilogue
+//   warps 0-3   softmax of stream 0  } one thread per query row.  A block is taken as two halves of 64 keys, each
+//   warps 4-7   softmax of stream 1  } an online-softmax step: the half's scores come out of TMEM once (two
+//                                      32-column loads in flight) and stay in registers for the row max (8
+//                                      independent chains) and the exp2; P packed to 16-bit goes back into S
+//                                      columns already read; lazy rescale of O only when the max grew by more
+//                                      than 2^8; the row sum of the item's last block goes to shared memory for
+//                                      the epilogue
 //   warps 8-11  epilogue of both streams: O / l from TMEM -> global memory, hands the O buffer back
 //   warps 12,14 TMA loader of stream 0 / 1 (lane 0 issues): Q, then K_j, V_j in list order, one TMA
 //               instruction per 128x128 tile
@@ -23,7 +25,7 @@
 // Lists are walked from the last entry (the diagonal block when causal, which usually holds the row
 // maximum) to the first, so the running maximum settles at the first block and O is rarely rescaled.
 // The kernel is a template over how a stream walks a 128-key block (see kHalfModeMinBlocksX2): as one block
-// (K and V as 32 KiB tiles, whole-block softmax: the shortest chain per item, for short lists), or as two
+// (K and V as 32 KiB tiles, one Q.K^T per block: the shortest chain per item, for short lists), or as two
 // 64-key halves (S of half h in its own 64-column TMEM buffer, so while the softmax warpgroup works on one half
 // the tensor pipe computes the other half's S and the previous half's P.V; K and V as four 16 KiB half-tiles
 // per block: for long lists).  Every CTA picks one of the two from its own list lengths.
@@ -371,10 +373,12 @@ __device__ __forceinline__ void attn_cta(const CUtensorMap& tmQ, const CUtensorM
           mma_ts(od, sd, dv[0], idesc_pv, j > 0 ? 1u : 0u);
 #pragma unroll
           for (int k = 1; k < 4; ++k) mma_ts(od, sd + k * 8, dv[k], idesc_pv, 1u);
+          mma_commit(bar(s, PV_DONE));                  // (a softmax warp that has to rescale O waits for this)
           if (!mbar_wait(bar(s, P_READY + 1), bc & 1, abort_flag)) { ok = false; break; }
           tc_fence_after();
 #pragma unroll
           for (int k = 4; k < 8; ++k) mma_ts(od, sd + k * 8, dv[k], idesc_pv, 1u);
+          mma_commit(bar(s, PV_DONE));
           mma_commit(bar(s, H_EMPTY + 2));
           if (j == n - 1) mma_commit(bar(s, O_FULL));
         }
@@ -436,8 +440,9 @@ __device__ __forceinline__ void attn_cta(const CUtensorMap& tmQ, const CUtensorM
           float mx8[8];
 #pragma unroll
           for (int q = 0; q < 8; ++q) mx8[q] = -INFINITY;
+          // the half's 64 scores stay in registers for both passes: one tensor-memory round trip per half
+          uint32_t v0[32], v1[32];
           {
-            uint32_t v0[32], v1[32];
             tmem_ld32(ts, v0);
             tmem_ld32(ts + 32, v1);
             tc_wait_ld();
@@ -509,14 +514,8 @@ __device__ __forceinline__ void attn_cta(const CUtensorMap& tmQ, const CUtensorM
             }
             tmem_st16(ts + c * 16, pk);
           };
-          {
-            uint32_t va[32], vb[32];
-            tmem_ld32(ts, va);
-            tmem_ld32(ts + 32, vb);
-            tc_wait_ld();
-            chunk(va, 0);
-            chunk(vb, 1);
-          }
+          chunk(v0, 0);
+          chunk(v1, 1);
           {
             float a0, a1;
             unpack_f32x2(add_f32x2(add_f32x2(ls2[0], ls2[1]), add_f32x2(ls2[2], ls2[3])), a0, a1);
@@ -571,180 +570,115 @@ __device__ __forceinline__ void attn_cta(const CUtensorMap& tmQ, const CUtensorM
         }
         const int k0 = __shfl_sync(0xffffffffu, w, j & 31) * 128;
         if (lane == 0) XB_TRACE_EV(0x38, bc);
-        const int limit = row_last - k0;                // columns c <= limit are visible
-        const bool masked = __any_sync(0xffffffffu, limit < 127);
         if (lane == 0) XB_TRACE_EV(0x30, bc);
         // waits are made warp-uniform: the tensor-memory loads/stores below are warp-collective
         if (!__all_sync(0xffffffffu, mbar_wait(s_full, bc & 1, abort_flag))) { ok = false; break; }
         tc_fence_after();
         if (lane == 0) XB_TRACE_EV(0x31, bc);
-        // ---- pass 1: row maximum, 8 independent chains of 3-input max.  In a masked block (diagonal / tail)
-        // each 32-column chunk is classified per warp: all visible, none visible, or mixed (per-element
-        // select).  The chunk loops are kept rolled: the kernel is bound by instruction issue and a small
-        // loop body measured faster than a fully unrolled one.
-        float mx8[8];
-#pragma unroll
-        for (int q = 0; q < 8; ++q) mx8[q] = -INFINITY;
-        uint32_t cls_mixed = 0u, cls_none = 0u;        // bit c4
-        if (masked) {
-#pragma unroll
-          for (int c4 = 0; c4 < 4; ++c4) {
-            const bool all_vis = __all_sync(0xffffffffu, limit - 32 * c4 >= 31);
-            const bool none_vis = __all_sync(0xffffffffu, limit - 32 * c4 < 0);
-            if (none_vis) cls_none |= 1u << c4;
-            else if (!all_vis) cls_mixed |= 1u << c4;
-          }
-        }
-        if (!masked) {
-          // two tensor-memory loads in flight per wait
-#pragma unroll 1
-          for (int c2 = 0; c2 < 2; ++c2) {
-            uint32_t v0[32], v1[32];
-            tmem_ld32(ts + c2 * 64, v0);
-            tmem_ld32(ts + c2 * 64 + 32, v1);
-            tc_wait_ld();
-#pragma unroll
-            for (int k = 0; k < 16; ++k) {
-              mx8[k & 7] = max3(mx8[k & 7], __uint_as_float(v0[2 * k]), __uint_as_float(v0[2 * k + 1]));
-              mx8[(k + 4) & 7] = max3(mx8[(k + 4) & 7], __uint_as_float(v1[2 * k]), __uint_as_float(v1[2 * k + 1]));
-            }
-          }
-        }
-#pragma unroll 1
-        for (int c4 = masked ? 0 : 4; c4 < 4; ++c4) {
-          if ((cls_none >> c4) & 1u) continue;
-          uint32_t v[32];
-          tmem_ld32(ts + c4 * 32, v);
-          tc_wait_ld();
-          if (!((cls_mixed >> c4) & 1u)) {
-#pragma unroll
-            for (int k = 0; k < 16; ++k)
-              mx8[k & 7] = max3(mx8[k & 7], __uint_as_float(v[2 * k]), __uint_as_float(v[2 * k + 1]));
-          } else {
-            const int lim4 = limit - 32 * c4;
-#pragma unroll
-            for (int k = 0; k < 16; ++k)
-              mx8[k & 7] = max3(mx8[k & 7], 2 * k <= lim4 ? __uint_as_float(v[2 * k]) : -INFINITY,
-                                2 * k + 1 <= lim4 ? __uint_as_float(v[2 * k + 1]) : -INFINITY);
-          }
-        }
-        const float mx = fmaxf(max3(mx8[0], mx8[1], mx8[2]), max3(max3(mx8[3], mx8[4], mx8[5]), mx8[6], mx8[7]));
-        const float m_new = fmaxf(m_used, mx * p.scale_log2);
-        const bool need = m_new > m_used + kRescaleThreshold || (j == 0) || (m_used == -INFINITY && m_new > -INFINITY);
-        if (__any_sync(0xffffffffu, need)) {
-          const float alpha = !need ? 1.f : (m_used == -INFINITY ? 0.f : fast_exp2(m_used - m_new));
-          if (j > 0) {
-            // S of block j is complete, and the tensor pipe runs in order, so the P.V of block j-1 of this
-            // stream has completed too: O may be touched
-            if (lane == 0) XB_TRACE_EV(0x32, bc);
-#pragma unroll
-            for (int c4 = 0; c4 < 4; ++c4) {
-              uint32_t v[32];
-              tmem_ld32(tmem_o + c4 * 32, v);
-              tc_wait_ld();
-#pragma unroll
-              for (int k = 0; k < 32; ++k) v[k] = __float_as_uint(__uint_as_float(v[k]) * alpha);
-              tmem_st32(tmem_o + c4 * 32, v);
-            }
-          }
-          l *= alpha;
-          if (need) m_used = m_new;
-        }
-        const float m_ref = m_used == -INFINITY ? 0.f : m_used;
-        if (lane == 0) XB_TRACE_EV(0x35, bc);
-        // ---- pass 2: exp2 in 32-column chunks; P chunk c4 (16 packed columns) overwrites S columns that were
-        // read already (packed column c/2 <= c)
+        // The block's 128 scores are taken in two halves of 64 columns, each an online-softmax step of its own:
+        // one tensor-memory round trip per half (both 32-column loads in flight), the 64 scores stay in registers
+        // for the maximum and for the exponentiation, and P of keys 0-63 is handed to the tensor pipe while keys
+        // 64-127 are still being worked on.  P (16-bit, two keys per column) of half h goes to columns
+        // [32h, 32h + 32), which hold scores that are in registers by then.
         const unsigned long long scale2 = pack_f32x2(p.scale_log2, p.scale_log2);
-        const unsigned long long nmref2 = pack_f32x2(-m_ref, -m_ref);
-        unsigned long long ls2[4];
-#pragma unroll
-        for (int q = 0; q < 4; ++q) ls2[q] = 0ull;     // (+0.f, +0.f)
-        if (!masked) {
-          // the load of the next 32 columns is in flight while the current ones are exponentiated
-          auto chunk = [&](const uint32_t (&v)[32], int c4) {
-            uint32_t pk[16];
-#pragma unroll
-            for (int k = 0; k < 16; ++k) {
-              float y0, y1;
-              unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(v[2 * k]), __uint_as_float(v[2 * k + 1])), scale2, nmref2),
-                           y0, y1);
-              const float p0 = fast_exp2(y0), p1 = fast_exp2(y1);
-              ls2[k & 3] = add_f32x2(ls2[k & 3], pack_f32x2(p0, p1));
-              pk[k] = pack16(p0, p1, p.is_bf16);
-            }
-            tmem_st16(ts + c4 * 16, pk);
-          };
-          uint32_t va[32], vb[32];
-          tmem_ld32(ts, va);
 #pragma unroll 1
-          for (int c2 = 0; c2 < 2; ++c2) {
-            tc_wait_ld();
-            tmem_ld32(ts + (2 * c2 + 1) * 32, vb);
-            chunk(va, 2 * c2);
-            tc_wait_ld();
-            if (c2 == 0) tmem_ld32(ts + 64, va);
-            chunk(vb, 2 * c2 + 1);
-            if (c2 == 0) {
-              // P of keys 0-63 is complete: their half of P.V may start
-              tc_wait_st();
-              tc_fence_before();
-              mbar_arrive(bar(s, P_READY));
-            }
-          }
-        }
-#pragma unroll 1
-        for (int c4 = masked ? 0 : 4; c4 < 4; ++c4) {
-          if (c4 == 2) {
-            tc_wait_st();
-            tc_fence_before();
-            mbar_arrive(bar(s, P_READY));
-          }
-          uint32_t pk[16];
-          if ((cls_none >> c4) & 1u) {
+        for (int h = 0; h < 2; ++h) {
+          const int limit = row_last - k0 - 64 * h;       // columns c <= limit of this half are visible
+          const bool none_vis = __all_sync(0xffffffffu, limit < 0);
+          const bool masked = __any_sync(0xffffffffu, limit < 63);
+          if (none_vis) {
+            // (the upper half of the diagonal block for the first 64 rows) P = 0, nothing else changes
+            uint32_t z[16];
 #pragma unroll
-            for (int k = 0; k < 16; ++k) pk[k] = 0u;
-            tmem_st16(ts + c4 * 16, pk);
-            continue;
-          }
-          uint32_t v[32];
-          tmem_ld32(ts + c4 * 32, v);
-          tc_wait_ld();
-          if (!((cls_mixed >> c4) & 1u)) {
-#pragma unroll
-            for (int k = 0; k < 16; ++k) {
-              float y0, y1;
-              unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(v[2 * k]), __uint_as_float(v[2 * k + 1])), scale2, nmref2),
-                           y0, y1);
-              const float p0 = fast_exp2(y0), p1 = fast_exp2(y1);
-              ls2[k & 3] = add_f32x2(ls2[k & 3], pack_f32x2(p0, p1));
-              pk[k] = pack16(p0, p1, p.is_bf16);
-            }
+            for (int k = 0; k < 16; ++k) z[k] = 0u;
+            tmem_st16(ts + h * 32, z);
+            tmem_st16(ts + h * 32 + 16, z);
           } else {
-            const int lim4 = limit - 32 * c4;
+            float mx8[8];
 #pragma unroll
-            for (int k = 0; k < 16; ++k) {
-              const float x0 = 2 * k <= lim4 ? __uint_as_float(v[2 * k]) : -INFINITY;
-              const float x1 = 2 * k + 1 <= lim4 ? __uint_as_float(v[2 * k + 1]) : -INFINITY;
-              float y0, y1;
-              unpack_f32x2(fma_f32x2(pack_f32x2(x0, x1), scale2, nmref2), y0, y1);
-              const float p0 = fast_exp2(y0), p1 = fast_exp2(y1);
-              ls2[k & 3] = add_f32x2(ls2[k & 3], pack_f32x2(p0, p1));
-              pk[k] = pack16(p0, p1, p.is_bf16);
+            for (int q = 0; q < 8; ++q) mx8[q] = -INFINITY;
+            uint32_t v0[32], v1[32];
+            tmem_ld32(ts + h * 64, v0);
+            tmem_ld32(ts + h * 64 + 32, v1);
+            tc_wait_ld();
+            if (!masked) {
+#pragma unroll
+              for (int k = 0; k < 16; ++k) {
+                mx8[k & 7] = max3(mx8[k & 7], __uint_as_float(v0[2 * k]), __uint_as_float(v0[2 * k + 1]));
+                mx8[(k + 4) & 7] = max3(mx8[(k + 4) & 7], __uint_as_float(v1[2 * k]), __uint_as_float(v1[2 * k + 1]));
+              }
+            } else {
+#pragma unroll
+              for (int k = 0; k < 16; ++k) {
+                mx8[k & 7] = max3(mx8[k & 7], 2 * k <= limit ? __uint_as_float(v0[2 * k]) : -INFINITY,
+                                  2 * k + 1 <= limit ? __uint_as_float(v0[2 * k + 1]) : -INFINITY);
+                mx8[(k + 4) & 7] = max3(mx8[(k + 4) & 7], 32 + 2 * k <= limit ? __uint_as_float(v1[2 * k]) : -INFINITY,
+                                        33 + 2 * k <= limit ? __uint_as_float(v1[2 * k + 1]) : -INFINITY);
+              }
             }
+            const float mx = fmaxf(max3(mx8[0], mx8[1], mx8[2]), max3(max3(mx8[3], mx8[4], mx8[5]), mx8[6], mx8[7]));
+            const float m_new = fmaxf(m_used, mx * p.scale_log2);
+            const bool first = j == 0 && h == 0;
+            const bool need = m_new > m_used + kRescaleThreshold || first || (m_used == -INFINITY && m_new > -INFINITY);
+            if (__any_sync(0xffffffffu, need)) {
+              const float alpha = !need ? 1.f : (m_used == -INFINITY ? 0.f : fast_exp2(m_used - m_new));
+              if (!first) {
+                // O may be touched once every P.V issued so far for this stream has completed (the half before
+                // this one is the latest: its P.V cannot have been issued before this half's P is ready)
+                if (lane == 0) XB_TRACE_EV(0x32, bc);
+                const uint32_t hq = bc * 2 + h;
+                if (!__all_sync(0xffffffffu, mbar_wait(bar(s, PV_DONE), (hq - 1) & 1, abort_flag))) { ok = false; break; }
+                tc_fence_after();
+#pragma unroll 1
+                for (int c4 = 0; c4 < 4; ++c4) {
+                  uint32_t v[32];
+                  tmem_ld32(tmem_o + c4 * 32, v);
+                  tc_wait_ld();
+#pragma unroll
+                  for (int k = 0; k < 32; ++k) v[k] = __float_as_uint(__uint_as_float(v[k]) * alpha);
+                  tmem_st32(tmem_o + c4 * 32, v);
+                }
+              }
+              l *= alpha;
+              if (need) m_used = m_new;
+            }
+            const float m_ref = m_used == -INFINITY ? 0.f : m_used;
+            if (lane == 0) XB_TRACE_EV(0x35, bc);
+            const unsigned long long nmref2 = pack_f32x2(-m_ref, -m_ref);
+            unsigned long long ls2[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) ls2[q] = 0ull;     // (+0.f, +0.f)
+            auto chunk = [&](const uint32_t (&v)[32], int c) {
+              uint32_t pk[16];
+              const int lim = limit - 32 * c;
+#pragma unroll
+              for (int k = 0; k < 16; ++k) {
+                float x0 = __uint_as_float(v[2 * k]), x1 = __uint_as_float(v[2 * k + 1]);
+                if (masked) {
+                  x0 = 2 * k <= lim ? x0 : -INFINITY;
+                  x1 = 2 * k + 1 <= lim ? x1 : -INFINITY;
+                }
+                float y0, y1;
+                unpack_f32x2(fma_f32x2(pack_f32x2(x0, x1), scale2, nmref2), y0, y1);
+                const float p0 = fast_exp2(y0), p1 = fast_exp2(y1);
+                ls2[k & 3] = add_f32x2(ls2[k & 3], pack_f32x2(p0, p1));
+                pk[k] = pack16(p0, p1, p.is_bf16);
+              }
+              tmem_st16(ts + h * 32 + c * 16, pk);
+            };
+            chunk(v0, 0);
+            chunk(v1, 1);
+            float a0, a1;
+            unpack_f32x2(add_f32x2(add_f32x2(ls2[0], ls2[1]), add_f32x2(ls2[2], ls2[3])), a0, a1);
+            l += a0 + a1;
           }
-          tmem_st16(ts + c4 * 16, pk);
+          if (j == n - 1 && h == 1) s_l[(s * 2 + (m & 1)) * 128 + r] = l;   // read by the epilogue once this item's last P.V is done
+          tc_wait_st();
+          tc_fence_before();
+          mbar_arrive(bar(s, P_READY + h));
+          if (lane == 0) XB_TRACE_EV(0x33, bc * 2 + h);
         }
-        {
-          float a0, a1, b0, b1;
-          unpack_f32x2(add_f32x2(add_f32x2(ls2[0], ls2[1]), add_f32x2(ls2[2], ls2[3])), a0, a1);
-          (void)b0; (void)b1;
-          l += a0 + a1;
-        }
-        if (j == n - 1) s_l[(s * 2 + (m & 1)) * 128 + r] = l;   // read by the epilogue once this item's last P.V is done
-        tc_wait_st();
-        tc_fence_before();
-        mbar_arrive(bar(s, P_READY + 1));
-        if (lane == 0) XB_TRACE_EV(0x33, bc);
+        if (!ok) break;
       }
       it = nit; n = nn; win = nwin;
     }
@@ -1082,12 +1016,9 @@ int block_sparse_attn_launch(const void* q, const void* k, const void* v, int dt
                                             &rest, &pair_header, min_share, status, stream)))
       return rc;
   }
-  if (rest)
-    return launch_dependent(block_sparse_attn_kernel, dim3(grid), dim3(kAttnThreads), kAttnSmem, stream, tmQ, tmK, tmV,
-                            tmKf, tmVf, p, block_idx, block_cnt, rest, pair_header, min_share, out, status);
-  block_sparse_attn_kernel<<<grid, kAttnThreads, kAttnSmem, stream>>>(tmQ, tmK, tmV, tmKf, tmVf, p, block_idx, block_cnt,
-                                                                      rest, pair_header, min_share, out, status);
-  return launch_status();
+  // (a dependent launch in every case: after the pair kernel, or after whatever kernel produced the block lists)
+  return launch_dependent(block_sparse_attn_kernel, dim3(grid), dim3(kAttnThreads), kAttnSmem, stream, tmQ, tmK, tmV,
+                          tmKf, tmVf, p, block_idx, block_cnt, rest, pair_header, min_share, out, status);
 }
 
 }  // namespace xb
