@@ -25,6 +25,7 @@
 namespace xb {
 
 constexpr int kPeelMax = 24;
+constexpr int kPeelProbe = 8;
 
 struct SelParams {
   int batch, heads, q_blocks, k_blocks;
@@ -53,12 +54,70 @@ __device__ __forceinline__ uint32_t bits_le(int hi, int t) {
   return r < 0 ? 0u : (r >= 31 ? 0xffffffffu : (2u << r) - 1u);
 }
 
+// Bitonic sort, descending, of the np2 = 32 * SEG keys of a row by one warp, in registers: lane l holds the
+// positions [l * SEG, (l + 1) * SEG).  Compare-exchanges between positions of one lane are register moves, those
+// between lanes one 64-bit shuffle; nothing goes through shared memory until the sorted keys are written out
+// (the same network run on a shared-memory array costs a warp barrier and two round trips per stage: 150 us for
+// a 1024-key row, most of the selection time on non-causal masks whose rows are flat).
+template <int SEG>
+__device__ __forceinline__ void warp_sort_desc(unsigned long long* __restrict__ keys, const float* __restrict__ cval,
+                                               const uint16_t* __restrict__ cidx, int M, int lane) {
+  unsigned long long kr[SEG];
+#pragma unroll
+  for (int r = 0; r < SEG; ++r) {
+    const int t = lane * SEG + r;
+    unsigned long long key = 0ull;
+    if (t < M && cval[t] > 0.f)
+      key = (static_cast<unsigned long long>(__float_as_uint(cval[t])) << 32) | (0xFFFFFFFFull - cidx[t]);
+    kr[r] = key;
+  }
+  constexpr int np2 = 32 * SEG;
+#pragma unroll 1
+  for (int k = 2; k <= np2; k <<= 1) {
+    // partners in other lanes (distance j >= SEG): the lower position keeps the larger key where the run descends
+#pragma unroll 1
+    for (int j = k >> 1; j >= SEG; j >>= 1) {
+      const int lane_bit = j / SEG;
+      const bool lower = (lane & lane_bit) == 0;
+#pragma unroll
+      for (int r = 0; r < SEG; ++r) {
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, kr[r], lane_bit);
+        const bool desc = ((lane * SEG + r) & k) == 0;
+        const unsigned long long hi = kr[r] > other ? kr[r] : other, lo = kr[r] > other ? other : kr[r];
+        kr[r] = (lower == desc) ? hi : lo;
+      }
+    }
+    // partners inside the lane (distance jj < SEG)
+#pragma unroll
+    for (int jj = SEG / 2; jj > 0; jj >>= 1) {
+      if (jj < k) {
+#pragma unroll
+        for (int r = 0; r < SEG; ++r) {
+          if ((r & jj) == 0) {
+            const bool desc = ((lane * SEG + r) & k) == 0;
+            const unsigned long long a = kr[r], b = kr[r | jj];
+            const bool swap = desc ? (a < b) : (a > b);
+            kr[r] = swap ? b : a;
+            kr[r | jj] = swap ? a : b;
+          }
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < SEG; ++r) keys[lane * SEG + r] = kr[r];
+  __syncwarp();
+}
+
 // One warp per row.  The row is read once (16-byte loads): fp64 total, the forced blocks, and the positive
 // scores compacted in column order into shared memory (score rows are sparse: most blocks hold no mass).
 // Zero-score columns are not stored: all of them rank after the positive ones, in column order, and the rule
 // can only take the first of them or all of them (see below).  Taken columns are a bitmap, so the mask row and
 // the ascending block list are produced word by word.
-__global__ void select_kernel(const float* __restrict__ sums, const SelParams p,
+// kMaxSeg: the longest row the register sort is compiled for, in keys per lane (4 / 16 / 32: rows of up to 128 /
+// 512 / 1024 key blocks; the kernel's register count, and with it the warps per SM, follows the largest one).
+template <int kMaxSeg>
+__global__ void __launch_bounds__(256) select_kernel(const float* __restrict__ sums, const SelParams p,
                               const float* __restrict__ thr_per_head, uint8_t* __restrict__ mask_out,
                               int32_t* __restrict__ idx_out, int32_t* __restrict__ cnt_out, int* status) {
   extern __shared__ __align__(16) uint8_t sel_smem[];
@@ -177,6 +236,9 @@ __global__ void select_kernel(const float* __restrict__ sums, const SelParams p,
     while (live > 0 && i <= kPeelMax) {
       const double c = lag ? (i == 1 ? 0.0 : fsum + s_lag) : fsum + s_cur;
       if (!(c < req)) { untaken = true; stop = true; break; }
+      // a flat row (the eight largest scores hold less than a third of the mass wanted) will need far more ranks
+      // than this loop is meant for: sort the rest right away (the sort continues from any state of this loop)
+      if (i == kPeelProbe + 1 && (fsum + s_cur) * 3.0 < req) break;
       float bv = -1.f;
       int bp = 0x7fffffff;
       for (int t = lane; t < M; t += 32) {
@@ -205,24 +267,38 @@ __global__ void select_kernel(const float* __restrict__ sums, const SelParams p,
       {
         int np2 = 32;
         while (np2 < M) np2 <<= 1;
-        for (int t = lane; t < np2; t += 32) {
-          unsigned long long key = 0ull;
-          if (t < M && cval[t] > 0.f)
-            key = (static_cast<unsigned long long>(__float_as_uint(cval[t])) << 32) | (0xFFFFFFFFull - cidx[t]);
-          keys[t] = key;
-        }
-        __syncwarp();
-        for (int k = 2; k <= np2; k <<= 1) {
-          for (int j = k >> 1; j > 0; j >>= 1) {
-            for (int t = lane; t < np2; t += 32) {
-              const int ixj = t ^ j;
-              if (ixj > t) {
-                const unsigned long long a = keys[t], b = keys[ixj];
-                const bool desc = (t & k) == 0;
-                if (desc ? (a < b) : (a > b)) { keys[t] = b; keys[ixj] = a; }
+        if (np2 <= 32 * kMaxSeg) {
+          if (np2 == 32) warp_sort_desc<1>(keys, cval, cidx, M, lane);
+          else if (np2 == 64) warp_sort_desc<2>(keys, cval, cidx, M, lane);
+          else if (np2 == 128) warp_sort_desc<4>(keys, cval, cidx, M, lane);
+          if constexpr (kMaxSeg >= 16) {
+            if (np2 == 256) warp_sort_desc<8>(keys, cval, cidx, M, lane);
+            else if (np2 == 512) warp_sort_desc<16>(keys, cval, cidx, M, lane);
+          }
+          if constexpr (kMaxSeg >= 32) {
+            if (np2 == 1024) warp_sort_desc<32>(keys, cval, cidx, M, lane);
+          }
+        } else {
+          // longer rows: the same network on the shared-memory array
+          for (int t = lane; t < np2; t += 32) {
+            unsigned long long key = 0ull;
+            if (t < M && cval[t] > 0.f)
+              key = (static_cast<unsigned long long>(__float_as_uint(cval[t])) << 32) | (0xFFFFFFFFull - cidx[t]);
+            keys[t] = key;
+          }
+          __syncwarp();
+          for (int k = 2; k <= np2; k <<= 1) {
+            for (int j = k >> 1; j > 0; j >>= 1) {
+              for (int t = lane; t < np2; t += 32) {
+                const int ixj = t ^ j;
+                if (ixj > t) {
+                  const unsigned long long a = keys[t], b = keys[ixj];
+                  const bool desc = (t & k) == 0;
+                  if (desc ? (a < b) : (a > b)) { keys[t] = b; keys[ixj] = a; }
+                }
               }
+              __syncwarp();
             }
-            __syncwarp();
           }
         }
         const int seg = np2 / 32;                  // contiguous positions per lane
@@ -425,13 +501,16 @@ int select_launch(const float* attn_sums, int batch, int heads, int q_blocks, in
   if (rows > 0x7fffffffLL) return XATTN_B200_ERR_LIMIT;
   p.rows_total = static_cast<int>(rows);
   const size_t smem = static_cast<size_t>(wpc) * p.per_warp_bytes;
-  if (smem > 48 * 1024 &&
-      cudaFuncSetAttribute(select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) !=
-          cudaSuccess)
-    return XATTN_B200_ERR_CUDA;
   const int grid = static_cast<int>((rows + wpc - 1) / wpc);
-  select_kernel<<<grid, wpc * 32, smem, stream>>>(attn_sums, p, thr_per_head, mask, block_idx, block_cnt, status);
-  return launch_status();
+  auto launch = [&](auto kern) -> int {
+    if (smem > 48 * 1024 &&
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
+      return XATTN_B200_ERR_CUDA;
+    kern<<<grid, wpc * 32, smem, stream>>>(attn_sums, p, thr_per_head, mask, block_idx, block_cnt, status);
+    return launch_status();
+  };
+  // the instantiation whose flat-row sort holds just enough keys per lane in registers for this row length
+  return np2 > 512 ? launch(select_kernel<32>) : (np2 > 128 ? launch(select_kernel<16>) : launch(select_kernel<4>));
 }
 
 int mask_to_lists_launch(const uint8_t* mask, int batch, int heads, int mask_q_blocks, int mask_k_blocks, int q_len,
