@@ -246,14 +246,14 @@ def mask_to_lists(mask: torch.Tensor, q_len: int, k_len: int, causal: bool):
 
 # ------------------------------------------------------------------------------ phase 3
 # The split has fixed costs: the classify kernel (8 us) and the general kernel's pass over the rows the pair kernel
-# leaves (a few items per SM, each a full latency chain: 30-65 us), against 8-12 % of the call won when 95 % of the
-# blocks qualify (Llama-3.1-8B at 128K tokens); and an attempt that the library declines costs 30-45 us (at 32K or
-# 64K tokens it does decline: 66 % / 89 % qualify).  So the scratch memory is offered by default only for sequences
-# of at least 96K tokens (PAIR_MIN_K_BLOCKS key blocks) and calls of at least PAIR_MIN_ITEMS (batch, query head,
-# query block) items: the whole 128K-token layer (32 768 items) but not a rank's two kv heads of it (8 192 items,
-# where the general kernel alone takes 0.21 ms).
+# leaves (a few items per SM, each a full latency chain), against 8-12 % of the call won when 95 % of the blocks
+# qualify (Llama-3.1-8B at 128K tokens); and an attempt that the library declines costs 15-45 us (at 32K or 64K
+# tokens it does decline: 66 % / 89 % qualify).  Measured on 1 / 2 / 4 / 8 kv heads of the 128K-token layer (4096 /
+# 8192 / 16384 / 32768 items): general kernel alone 117 / 221 / 430 / 830 us, with the split 134 / 219 / 393 / 750.
+# So the scratch memory is offered by default only for sequences of at least 96K tokens (PAIR_MIN_K_BLOCKS key
+# blocks) and calls of at least PAIR_MIN_ITEMS (batch, query head, query block) items.
 PAIR_MIN_K_BLOCKS = 768
-PAIR_MIN_ITEMS = 24576
+PAIR_MIN_ITEMS = 12288
 # Non-causal calls: sorting the items by list length is one launch of a few microseconds; with only a few items per
 # SM there is nothing to balance.
 ORDER_MIN_ITEMS = 16 * 148
