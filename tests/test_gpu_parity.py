@@ -865,7 +865,9 @@ def test_llama_rope_and_attend_equals_the_composed_reference_steps():
                                              ("llama3_8b_32k", 8192, 4096, 4096), ("llama3_8b_32k", 6144, 6144, 2048)])
 def test_chunk_band_layout_equals_the_dense_one(name, L, Lq, chunk):
     """Un-padded causal keys under the torch branch: the sums kept as a chunk-wide band, and the selection run
-    on the band, give exactly the dense layout's sums, mask and block lists."""
+    on the band, give the dense layout's sums, mask and block lists.  The sums are bit-identical except where a
+    chunk is a single 128x128 tile (stride 16, chunk 2048): there the band layout's block sums are finished in the
+    GEMM's epilogue, which adds the rows of a query block in another order (agreement to the last few bits)."""
     from xattn_b200 import ops, synth
     q, k, v, w = synth.make_inputs(name, seed=11, heads_limit=1, seq_len=L)
     q, k = q[:, :, L - Lq:].to(DEV), k.to(DEV)
@@ -879,7 +881,12 @@ def test_chunk_band_layout_equals_the_dense_one(name, L, Lq, chunk):
         cur = g["block_offset"] + c * g["bpc"]
         rows = slice(c * g["bpc"], (c + 1) * g["bpc"])
         rebuilt[:, :, rows, cur:cur + g["bpc"]] = band[:, :, rows]
-    assert torch.equal(rebuilt, dense)
+    if chunk // w.stride == 128:
+        torch.testing.assert_close(rebuilt, dense, rtol=2e-6, atol=0.0)
+        assert torch.equal(rebuilt == 0, dense == 0)
+        dense = rebuilt                      # the selection is compared on the same numbers in both layouts
+    else:
+        assert torch.equal(rebuilt, dense)
     for thr, sink, recent in ((0.9, False, False), (torch.linspace(0.5, 1.0, q.shape[1]), False, False),
                               (0.7, True, True), (0.0, False, True), (1.0, True, False)):
         m0, i0, c0 = ops.select_blocks(dense, g["bpc"], g["block_offset"], thr, True, True, sink, recent,

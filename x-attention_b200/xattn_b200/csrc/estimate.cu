@@ -246,12 +246,104 @@ __device__ __forceinline__ void est_epilogue_row(const EstGeom& g, uint32_t tadd
   if (row_ok) *mslot = make_float2(m_scaled, tile_sum);
 }
 
-template <int RBS>
+// Epilogue for geometries in which a reshaped row sees a single 128-column tile (the torch branch with chunks of
+// 128 reshaped rows, e.g. 128K tokens at stride 16): the tile's row maximum and row sum ARE the row's, so the
+// normalised block sums are finished here -- exp2 against the row maximum, sums over groups of RBS columns kept in
+// registers, division by the row sum, and the sum over the RBS rows of a query block taken across lanes -- and
+// written to the chunk-band block sums directly.  Neither the per-row scratch nor the two kernels that would read
+// it are needed.  `out` is the 128 / RBS floats of this row's query block (written by its first row's lane).
+template <int RBS, typename Release>
+__device__ __forceinline__ void est_epilogue_row_direct(const EstGeom& g, uint32_t taddr, int clo, int chi,
+                                                        float* __restrict__ out, bool write, Release release) {
+  constexpr int kChunks = 4, kPer = 32 / RBS;               // 128 columns; key blocks per 32-column chunk
+  auto fully_visible = [&](int c8) { return __all_sync(0xffffffffu, clo <= c8 * 32 && chi >= c8 * 32 + 31); };
+  float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+  {
+    uint32_t va[32], vb[32];
+    tmem_ld32(taddr, va);
+#pragma unroll
+    for (int c8 = 0; c8 < kChunks; c8 += 2) {
+      tc_wait_ld();
+      tmem_ld32(taddr + (c8 + 1) * 32, vb);
+      auto max_chunk = [&](const uint32_t (&v)[32], int c) {
+        if (fully_visible(c)) {
+#pragma unroll
+          for (int k = 0; k < 32; ++k) mx4[k & 3] = fmaxf(mx4[k & 3], __uint_as_float(v[k]));
+        } else {
+#pragma unroll
+          for (int k = 0; k < 32; ++k) {
+            const int col = c * 32 + k;
+            if (col >= clo && col <= chi) mx4[k & 3] = fmaxf(mx4[k & 3], __uint_as_float(v[k]));
+          }
+        }
+      };
+      max_chunk(va, c8);
+      tc_wait_ld();
+      if (c8 + 2 < kChunks) tmem_ld32(taddr + (c8 + 2) * 32, va);
+      max_chunk(vb, c8 + 1);
+    }
+  }
+  const float m_scaled = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * g.scale_log2;     // scale > 0
+  float blk[kChunks * kPer];
+  float row_sum = 0.f;
+  {
+    uint32_t va[32], vb[32];
+    tmem_ld32(taddr, va);
+#pragma unroll
+    for (int c8 = 0; c8 < kChunks; c8 += 2) {
+      tc_wait_ld();
+      tmem_ld32(taddr + (c8 + 1) * 32, vb);
+      auto sum_chunk = [&](const uint32_t (&v)[32], int c) {
+        float gs[kPer];
+#pragma unroll
+        for (int q = 0; q < kPer; ++q) gs[q] = 0.f;
+        if (fully_visible(c)) {
+#pragma unroll
+          for (int k = 0; k < 32; ++k) gs[k / RBS] += fast_exp2(fmaf(__uint_as_float(v[k]), g.scale_log2, -m_scaled));
+        } else {
+#pragma unroll
+          for (int k = 0; k < 32; ++k) {
+            const int col = c * 32 + k;
+            const float x = fmaf(__uint_as_float(v[k]), g.scale_log2, -m_scaled);
+            gs[k / RBS] += (col >= clo && col <= chi) ? fast_exp2(x) : 0.f;
+          }
+        }
+#pragma unroll
+        for (int q = 0; q < kPer; ++q) {
+          row_sum += gs[q];
+          blk[c * kPer + q] = gs[q];
+        }
+      };
+      sum_chunk(va, c8);
+      tc_wait_ld();
+      if (c8 + 2 < kChunks) tmem_ld32(taddr + (c8 + 2) * 32, va);
+      else release();                                   // the tile's last load has completed
+      sum_chunk(vb, c8 + 1);
+    }
+  }
+  // normalise (a row that sees nothing contributes nothing), then add the RBS rows of the query block: they are RBS
+  // consecutive lanes
+  const float inv = row_sum > 0.f ? 1.f / row_sum : 0.f;
+#pragma unroll
+  for (int q = 0; q < kChunks * kPer; ++q) {
+    float v = blk[q] * inv;
+#pragma unroll
+    for (int o = 1; o < RBS; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    blk[q] = v;
+  }
+  if (write) {
+#pragma unroll
+    for (int q = 0; q < kChunks * kPer; q += 4)
+      *reinterpret_cast<float4*>(out + q) = make_float4(blk[q], blk[q + 1], blk[q + 2], blk[q + 3]);
+  }
+}
+
+template <int RBS, bool DIRECT>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 est_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmQt, const __grid_constant__ CUtensorMap tmKt, const EstGeom g,
                 const int* __restrict__ tile_lo, const int* __restrict__ tile_prefix, float* __restrict__ partial,
-                float2* __restrict__ mtile, const uint32_t idesc, int* status) {
+                float2* __restrict__ mtile, float* __restrict__ sums, const uint32_t idesc, int* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   // 128-column tiles (every operand tile is used once: the kernel streams Q and K from HBM) take six 32 KiB
@@ -377,14 +469,23 @@ est_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const bool row_ok = i < g.rows_total;
       const size_t rrow = static_cast<size_t>(bh) * g.rows_total + (row_ok ? i : 0);
       const int nlo = __ldg(tile_lo + mt);
-      est_epilogue_row<RBS>(g, taddr, n_chunks, clo, chi, row_ok,
-                            partial + rrow * g.p_pitch - scratch_block0(g, nlo), nt * kGroups,
-                            mtile + rrow * g.m_pitch + nt - scratch_tile0(g, nlo), [&]() {
-                              // all TMEM reads of this accumulator are done: hand it back to the MMA thread
-                              tc_fence_before();
-                              __syncwarp();
-                              if (lane == 0) mbar_arrive(tempty0 + 8 * acc);
-                            });
+      auto release = [&]() {
+        // all TMEM reads of this accumulator are done: hand it back to the MMA thread
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty0 + 8 * acc);
+      };
+      if constexpr (DIRECT) {
+        // the query block of this row, and its first row's lane as the writer (RBS divides 32)
+        const int qb = i / RBS;
+        est_epilogue_row_direct<RBS>(g, taddr, clo, chi,
+                                     sums + (static_cast<size_t>(bh) * g.qb_total + (qb < g.qb_total ? qb : 0)) * g.bpc,
+                                     (lane % RBS) == 0 && qb < g.qb_total, release);
+      } else {
+        est_epilogue_row<RBS>(g, taddr, n_chunks, clo, chi, row_ok,
+                              partial + rrow * g.p_pitch - scratch_block0(g, nlo), nt * kGroups,
+                              mtile + rrow * g.m_pitch + nt - scratch_tile0(g, nlo), release);
+      }
     }
   }
 
@@ -885,6 +986,20 @@ int estimate_launch(const void* q, const void* k, int dtype, int batch, int hq, 
 #ifdef XB_EST_NO_PAIRS
   use_pairs = false;
 #endif
+  // Chunks of exactly one 128-row, 128-column tile under the torch branch (128K tokens at stride 16): a row's only
+  // tile holds exactly the key blocks of its chunk-band output, so the GEMM's epilogue finishes the block sums
+  // itself and neither the scratch arrays nor est_rowstat_kernel / est_blocksum_kernel are needed.
+  bool direct = !use_pairs && g.band && g.left_blank && g.compact && g.m_pitch == 1 && g.tile_n == 128 &&
+                g.rcs == kTileM && g.row_off % 128 == 0 && g.rbs <= 32 && 32 % g.rbs == 0 &&
+                g.bpc == 128 / g.rbs && g.bpc % 4 == 0 && (reinterpret_cast<uintptr_t>(attn_sums) & 15) == 0;
+  for (int mt = 0; direct && mt < g.n_mtiles; ++mt) {
+    int first, count;
+    row_tile_range(g, mt, first, count);
+    direct = count == 1 && first * 128 == (mt * kTileM / g.rcs) * g.rcs + g.row_off;
+  }
+#ifdef XB_EST_NO_DIRECT
+  direct = false;
+#endif
   // ragged lengths: stage the tile with the last (partial) stride group and map it like the tensor itself
   CUtensorMap tmQt = tmQ, tmKt = tmK;
   auto stage_tail = [&](const void* src, int64_t sb, int64_t sh, int64_t sl, int heads, int len, int tile_rows,
@@ -967,15 +1082,25 @@ int estimate_launch(const void* q, const void* k, int dtype, int batch, int hq, 
   auto launch = [&](auto kern) -> int {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem) != cudaSuccess)
       return XATTN_B200_ERR_CUDA;
-    kern<<<grid, kGemmThreads, kGemmSmem, stream>>>(tmQ, tmK, tmQt, tmKt, g, tile_lo, tile_prefix, partial, mtile, idesc,
-                                                    status);
+    kern<<<grid, kGemmThreads, kGemmSmem, stream>>>(tmQ, tmK, tmQt, tmKt, g, tile_lo, tile_prefix, partial, mtile,
+                                                    attn_sums, idesc, status);
     return launch_status();
   };
+  if (direct) {
+    switch (g.rbs) {
+      case 4: rc = launch(est_gemm_kernel<4, true>); break;
+      case 8: rc = launch(est_gemm_kernel<8, true>); break;
+      case 16: rc = launch(est_gemm_kernel<16, true>); break;
+      case 32: rc = launch(est_gemm_kernel<32, true>); break;
+      default: rc = XATTN_B200_ERR_ARG;
+    }
+    return rc;                                         // the block sums are complete
+  }
   switch (g.rbs) {
-    case 4: rc = launch(est_gemm_kernel<4>); break;
-    case 8: rc = launch(est_gemm_kernel<8>); break;
-    case 16: rc = launch(est_gemm_kernel<16>); break;
-    case 32: rc = launch(est_gemm_kernel<32>); break;
+    case 4: rc = launch(est_gemm_kernel<4, false>); break;
+    case 8: rc = launch(est_gemm_kernel<8, false>); break;
+    case 16: rc = launch(est_gemm_kernel<16, false>); break;
+    case 32: rc = launch(est_gemm_kernel<32, false>); break;
     default: rc = XATTN_B200_ERR_ARG;
   }
   if (rc) return rc;
