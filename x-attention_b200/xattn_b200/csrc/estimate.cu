@@ -59,7 +59,17 @@ struct EstGeom {
   int q_tail_mt, k_tail_nt;
   int head_dim;
   float scale_log2;
+  // Tile tables of est_setup_kernel computed on the host and carried in the kernel parameters when they are small
+  // (tab_n = n_mtiles <= kTabTiles, e.g. 32 row tiles at 32K tokens, 64 at 128K): every kernel copies them into
+  // shared memory and est_setup_kernel is not launched.  Layout: tile_lo[kTabTiles], tile_prefix[kTabTiles + 1],
+  // pair_lo[kTabTiles / 2], pair_prefix[kTabTiles / 2 + 1].
+  int tab_n;
+  int tab[64 + 65 + 32 + 33];
 };
+constexpr int kTabTiles = 64;
+constexpr int kTabInts = kTabTiles + (kTabTiles + 1) + kTabTiles / 2 + (kTabTiles / 2 + 1);
+constexpr int kTabPrefix = kTabTiles, kTabPairLo = kTabPrefix + kTabTiles + 1, kTabPairPrefix = kTabPairLo + kTabTiles / 2;
+static_assert(kTabInts == 64 + 65 + 32 + 33, "EstGeom::tab");
 
 // Visible columns [lo, hi] of reshaped row i (empty when hi < lo).
 // causal, torch branch (Xattention.py:191-225): columns [chunk_start, chunk_start + i_local], minus the
@@ -137,6 +147,12 @@ __global__ void est_setup_kernel(EstGeom g, int* __restrict__ tile_lo, int* __re
   }
 }
 
+// Tables from the kernel parameters (EstGeom::tab) copied into shared memory by the whole CTA; the caller
+// synchronises the CTA before the first use.
+__device__ __forceinline__ void load_tables(const EstGeom& g, int* s_tab) {
+  for (int i = threadIdx.x; i < kTabInts; i += blockDim.x) s_tab[i] = g.tab[i];
+}
+
 // Tile number -> (batch*head, row-tile group, column tile).  With `interleave` > 1 (the query heads per kv head)
 // the heads of a kv group take the same (row, column) tile one after the other, so that the K tile they share is
 // read from DRAM once and found in L2 by the other heads: it matters when the kernel streams its operands from
@@ -158,10 +174,10 @@ __device__ __forceinline__ void decode_tile(int n_groups, const int* __restrict_
   int lo = 0, hi = n_groups;     // find mt with prefix[mt] <= rem < prefix[mt+1]
   while (hi - lo > 1) {
     const int mid = (lo + hi) >> 1;
-    if (__ldg(tile_prefix + mid) <= rem) lo = mid; else hi = mid;
+    if (tile_prefix[mid] <= rem) lo = mid; else hi = mid;
   }
   mt = lo;
-  nt = __ldg(tile_lo + mt) + rem - __ldg(tile_prefix + mt);
+  nt = tile_lo[mt] + rem - tile_prefix[mt];
 }
 
 // Epilogue of one accumulator tile for one row (thread): softmax statistics and un-normalised block sums of the
@@ -342,9 +358,15 @@ template <int RBS, bool DIRECT>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 est_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmQt, const __grid_constant__ CUtensorMap tmKt, const EstGeom g,
-                const int* __restrict__ tile_lo, const int* __restrict__ tile_prefix, float* __restrict__ partial,
+                const int* tile_lo, const int* tile_prefix, float* __restrict__ partial,
                 float2* __restrict__ mtile, float* __restrict__ sums, const uint32_t idesc, int* status) {
   extern __shared__ uint8_t smem_raw[];
+  __shared__ int s_tab[kTabInts];
+  if (g.tab_n) {                                  // (made visible by the __syncthreads() that ends the prologue)
+    load_tables(g, s_tab);
+    tile_lo = s_tab;
+    tile_prefix = s_tab + kTabPrefix;
+  }
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   // 128-column tiles (every operand tile is used once: the kernel streams Q and K from HBM) take six 32 KiB
   // stages, 256-column tiles four 48 KiB ones: 192 KiB in flight either way
@@ -384,7 +406,7 @@ est_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int tiles_per_head = __ldg(tile_prefix + g.n_mtiles);
+  const int tiles_per_head = tile_prefix[g.n_mtiles];
   const int total_tiles = tiles_per_head * g.batch * g.hq;
   const int k_steps = g.S * g.d_chunks;
   const int group = g.hq / g.hkv;
@@ -468,7 +490,7 @@ est_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const uint32_t taddr = tmem_base + acc * kTileN + (static_cast<uint32_t>(quad * 32) << 16);
       const bool row_ok = i < g.rows_total;
       const size_t rrow = static_cast<size_t>(bh) * g.rows_total + (row_ok ? i : 0);
-      const int nlo = __ldg(tile_lo + mt);
+      const int nlo = tile_lo[mt];
       auto release = [&]() {
         // all TMEM reads of this accumulator are done: hand it back to the MMA thread
         tc_fence_before();
@@ -524,9 +546,15 @@ template <int RBS>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 est_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmKh,
                      const __grid_constant__ CUtensorMap tmQt, const __grid_constant__ CUtensorMap tmKt,
-                     const EstGeom g, const int* __restrict__ pair_lo, const int* __restrict__ pair_prefix,
+                     const EstGeom g, const int* pair_lo, const int* pair_prefix,
                      float* __restrict__ partial, float2* __restrict__ mtile, const uint32_t idesc, int* status) {
   extern __shared__ uint8_t smem_raw[];
+  __shared__ int s_tab[kTabInts];
+  if (g.tab_n) {                                  // (made visible by the __syncthreads() that ends the prologue)
+    load_tables(g, s_tab);
+    pair_lo = s_tab + kTabPairLo;
+    pair_prefix = s_tab + kTabPairPrefix;
+  }
   // the same offset in both CTAs of the pair (the dynamic shared memory of a kernel starts at the same address
   // in every CTA), which the MMA descriptors rely on
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -567,7 +595,7 @@ est_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   const uint32_t tmem_base = *tmem_slot;
 
   const int n_groups = (g.n_mtiles + 1) / 2;
-  const int tiles_per_head = __ldg(pair_prefix + n_groups);
+  const int tiles_per_head = pair_prefix[n_groups];
   const int total_tiles = tiles_per_head * g.batch * g.hq;
   const int k_steps = g.S * g.d_chunks;
   const int group = g.hq / g.hkv;
@@ -653,7 +681,7 @@ est_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       const bool row_ok = i < g.rows_total;
       const size_t rrow = static_cast<size_t>(bh) * g.rows_total + (row_ok ? i : 0);
       // (compact scratch: both row tiles of a pair lie in one chunk and start at the pair's first column tile)
-      const int nlo = __ldg(pair_lo + pm);
+      const int nlo = pair_lo[pm];
       est_epilogue_row<RBS>(g, taddr, n_chunks, clo, chi, row_ok,
                             partial + rrow * g.p_pitch - scratch_block0(g, nlo), nt * kGroups,
                             mtile + rrow * g.m_pitch + nt - scratch_tile0(g, nlo), [&]() {
@@ -689,14 +717,15 @@ est_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 //   est_blocksum_kernel one thread per (query block, key block):
 //                       out[qb][kb] = sum_{i in qb} partial[i][kb] * 2^(m_{i,t(kb)} - m_i) / l_i
 __global__ void __launch_bounds__(256)
-est_rowstat_kernel(const EstGeom g, const int* __restrict__ tile_lo, const int* __restrict__ tile_prefix,
+est_rowstat_kernel(const EstGeom g, const int* tile_lo, const int* tile_prefix,
                    const float2* __restrict__ mtile, float2* __restrict__ rowstat, int total_rows) {
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total_rows) return;
   const int i = idx % g.rows_total;
   const int mt = i / kTileM;
-  const int nlo = tile_lo[mt];
-  const int ncnt = tile_prefix[mt + 1] - tile_prefix[mt];
+  // (the three table entries a row needs come straight from the kernel parameters when the tables are there)
+  const int nlo = g.tab_n ? g.tab[mt] : tile_lo[mt];
+  const int ncnt = g.tab_n ? g.tab[kTabPrefix + mt + 1] - g.tab[kTabPrefix + mt] : tile_prefix[mt + 1] - tile_prefix[mt];
   const float2* mrow = mtile + static_cast<size_t>(idx) * g.m_pitch + nlo - scratch_tile0(g, nlo);
   float m = -INFINITY, l = 0.f;
   if (i < g.rows_valid) {
@@ -716,7 +745,7 @@ est_rowstat_kernel(const EstGeom g, const int* __restrict__ tile_lo, const int* 
 // rows span at most eight column tiles.
 template <int VEC, bool FUSED>
 __global__ void __launch_bounds__(256)
-est_blocksum_kernel(const EstGeom g, const int* __restrict__ tile_lo, const int* __restrict__ tile_prefix,
+est_blocksum_kernel(const EstGeom g, const int* tile_lo, const int* tile_prefix,
                     const float* __restrict__ partial, const float2* __restrict__ mtile,
                     const float2* __restrict__ rowstat, float* __restrict__ sums) {
   __shared__ float2 s_stat[32];                            // FUSED: (m_i, 1/l_i) of the query block's rows (rbs <= 32)
@@ -724,8 +753,9 @@ est_blocksum_kernel(const EstGeom g, const int* __restrict__ tile_lo, const int*
   const int i0 = qb * g.rbs;
   if (FUSED) {
     const int mt_ = i0 / kTileM;
-    const int nlo_ = __ldg(tile_lo + mt_);
-    const int ncnt_ = __ldg(tile_prefix + mt_ + 1) - __ldg(tile_prefix + mt_);
+    const int nlo_ = g.tab_n ? g.tab[mt_] : tile_lo[mt_];
+    const int ncnt_ = g.tab_n ? g.tab[kTabPrefix + mt_ + 1] - g.tab[kTabPrefix + mt_]
+                              : tile_prefix[mt_ + 1] - tile_prefix[mt_];
     int rows_ = g.rows_valid - i0;
     rows_ = rows_ > g.rbs ? g.rbs : rows_;
     const int row = threadIdx.x >> 3, slot = threadIdx.x & 7;
@@ -752,8 +782,8 @@ est_blocksum_kernel(const EstGeom g, const int* __restrict__ tile_lo, const int*
   if (kb_local >= (g.band ? g.bpc : g.kb_total)) return;
   const int kb = cur + kb_local;
   const int mt = i0 / kTileM;
-  const int nlo = __ldg(tile_lo + mt);
-  const int ncnt = __ldg(tile_prefix + mt + 1) - __ldg(tile_prefix + mt);
+  const int nlo = g.tab_n ? g.tab[mt] : tile_lo[mt];
+  const int ncnt = g.tab_n ? g.tab[kTabPrefix + mt + 1] - g.tab[kTabPrefix + mt] : tile_prefix[mt + 1] - tile_prefix[mt];
   const int gpt = g.tile_n / g.rbs;                       // key blocks per tile (a multiple of 4)
   const int t = kb / gpt;
   float acc[VEC];
@@ -866,6 +896,7 @@ static int fill_geometry(int batch, int hq, int hkv, int q_len, int k_len, int h
   g.n_ntiles = (g.cols_total + g.tile_n - 1) / g.tile_n;
   g.scale_log2 = scale * 1.4426950408889634f;
   g.head_dim = head_dim;
+  g.tab_n = 0;
   g.q_tail_mt = q_len % stride ? (q_len / stride) / kTileM : -1;
   g.k_tail_nt = k_len % stride ? (k_len / stride) / g.tile_n : -1;
   g.compact = g.left_blank;
@@ -1029,8 +1060,36 @@ int estimate_launch(const void* q, const void* k, int dtype, int batch, int hq, 
                                            use_pairs ? 128 : static_cast<uint32_t>(g.tile_n), &tmKt)))
     return rc;
 
-  est_setup_kernel<<<1, 256, 2 * sizeof(int) * g.n_mtiles, stream>>>(g, tile_lo, tile_prefix, pair_lo, pair_prefix);
-  if ((rc = launch_status())) return rc;
+  if (g.n_mtiles <= kTabTiles) {
+    // few row tiles: the tables travel in the kernel parameters (the arithmetic of est_setup_kernel, on the host)
+    int* t_lo = g.tab, *t_prefix = g.tab + kTabPrefix, *p_lo = g.tab + kTabPairLo, *p_prefix = g.tab + kTabPairPrefix;
+    int cnt[kTabTiles];
+    int acc = 0;
+    for (int mt = 0; mt < g.n_mtiles; ++mt) {
+      row_tile_range(g, mt, t_lo[mt], cnt[mt]);
+      t_prefix[mt] = acc;
+      acc += cnt[mt];
+    }
+    t_prefix[g.n_mtiles] = acc;
+    const int n_pairs = (g.n_mtiles + 1) / 2;
+    acc = 0;
+    for (int pm = 0; pm < n_pairs; ++pm) {
+      int lo = 0x7fffffff, hi = -1;
+      for (int mt = 2 * pm; mt < 2 * pm + 2 && mt < g.n_mtiles; ++mt)
+        if (cnt[mt] > 0) {
+          lo = t_lo[mt] < lo ? t_lo[mt] : lo;
+          hi = t_lo[mt] + cnt[mt] - 1 > hi ? t_lo[mt] + cnt[mt] - 1 : hi;
+        }
+      p_lo[pm] = hi < 0 ? 0 : lo;
+      p_prefix[pm] = acc;
+      acc += hi < 0 ? 0 : hi - lo + 1;
+    }
+    p_prefix[n_pairs] = acc;
+    g.tab_n = g.n_mtiles;
+  } else {
+    est_setup_kernel<<<1, 256, 2 * sizeof(int) * g.n_mtiles, stream>>>(g, tile_lo, tile_prefix, pair_lo, pair_prefix);
+    if ((rc = launch_status())) return rc;
+  }
 
   const int sms = sm_count();
   if (use_pairs) {
