@@ -115,8 +115,9 @@ struct Sched {
 // block counts while it builds the schedule and calls the body meant for its average list length, so the
 // choice needs no host synchronisation.
 // twice the average number of listed blocks per non-empty item from which the half-block body pays off
-// (random masks with n blocks per row, 16 heads x 16K: n=2 full 473 / half 391 TFLOP/s, n=3 549 / 518,
-// n=4 603 / 629, n=8 709 / 797, n=24 801 / 945)
+// (random masks with n blocks per row, 16 heads x 16K, full / half body in TFLOP/s: n=3 583-596 / 532-542,
+// n=4 637-651 / 645-663, n=6 691-708 / 756-771, n=8 726-739 / 818-824; the 32K Llama mask with its masked diagonal
+// blocks, 2.5 blocks per row: 676 / 484)
 constexpr int kHalfModeMinBlocksX2 = 7;
 template <bool kHalf>
 __device__ __forceinline__ void attn_cta(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV,
