@@ -73,24 +73,36 @@ __global__ void pair_classify_kernel(const int32_t* __restrict__ block_idx, cons
     const int bg = u / q_blocks;
     const int g = bg % hkv, b = bg / hkv;
     const size_t row0 = (static_cast<size_t>(b) * hq + static_cast<size_t>(g) * group) * q_blocks + qb;
+    // The loads of the heads do not depend on each other (no early exit): a unit costs two memory round trips,
+    // counts then list heads, whatever the number of heads.  The first two list entries are read even when the
+    // list is shorter (they exist: a row of the index array has list_k_blocks >= 1 entries, and the second is
+    // only read when list_k_blocks >= 2); they are ignored then.
     const int c0 = __ldg(block_cnt + row0);
-    bool ok = c0 == 1 || c0 == 2;
-    int i0 = 0, i1 = 0;
-    if (ok) {
-      i0 = __ldg(block_idx + row0 * list_k_blocks);
-      i1 = c0 == 2 ? __ldg(block_idx + row0 * list_k_blocks + 1) : 0;
-      for (int j = 1; j < group && ok; ++j) {
-        const size_t row = row0 + static_cast<size_t>(j) * q_blocks;
-        ok = __ldg(block_cnt + row) == c0 && __ldg(block_idx + row * list_k_blocks) == i0 &&
-             (c0 == 1 || __ldg(block_idx + row * list_k_blocks + 1) == i1);
-      }
+    bool same_cnt = true;
+#pragma unroll 4
+    for (int j = 0; j < group; ++j) {
+      const int c = __ldg(block_cnt + row0 + static_cast<size_t>(j) * q_blocks);
+      same_cnt &= c == c0;
+      total += c;
     }
+    bool ok = same_cnt && (c0 == 1 || c0 == 2);
+    const bool two = list_k_blocks >= 2;
+    const int i0 = __ldg(block_idx + row0 * list_k_blocks);
+    const int i1 = two ? __ldg(block_idx + row0 * list_k_blocks + 1) : 0;
+    bool same_idx = true;
+#pragma unroll 4
+    for (int j = 1; j < group; ++j) {
+      const size_t row = row0 + static_cast<size_t>(j) * q_blocks;
+      const int a = __ldg(block_idx + row * list_k_blocks);
+      const int b2 = two ? __ldg(block_idx + row * list_k_blocks + 1) : 0;
+      same_idx &= a == i0 && (c0 == 1 || b2 == i1);
+    }
+    ok = ok && same_idx;
     if (ok) {
       const int pos = atomicAdd(counter, 1);
       list[pos].unit = u;
       list[pos].blocks = static_cast<uint32_t>(i0) | ((c0 == 2 ? static_cast<uint32_t>(i1) : kNoBlock) << 16);
     }
-    for (int j = 0; j < group; ++j) total += __ldg(block_cnt + row0 + static_cast<size_t>(j) * q_blocks);
     taken = ok ? total : 0;
     if (!ok) {
       // work item t of the general kernel: t = ((q_blocks - 1 - qb) * batch + b) * hq + h
