@@ -862,7 +862,8 @@ def test_llama_rope_and_attend_equals_the_composed_reference_steps():
 
 
 @pytest.mark.parametrize("name,L,Lq,chunk", [("llama3_8b_32k", 8192, 8192, 2048), ("llama3_8b_128k", 8192, 8192, 2048),
-                                             ("llama3_8b_32k", 8192, 4096, 4096), ("llama3_8b_32k", 6144, 6144, 2048)])
+                                             ("llama3_8b_32k", 8192, 4096, 4096), ("llama3_8b_32k", 6144, 6144, 2048),
+                                             ("llama3_8b_128k", 8192, 4096, 2048), ("llama3_8b_128k", 10240, 2048, 2048)])
 def test_chunk_band_layout_equals_the_dense_one(name, L, Lq, chunk):
     """Un-padded causal keys under the torch branch: the sums kept as a chunk-wide band, and the selection run
     on the band, give the dense layout's sums, mask and block lists.  The sums are bit-identical except where a
