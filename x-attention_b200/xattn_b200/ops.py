@@ -7,6 +7,7 @@ from __future__ import annotations
 
 import ctypes as C
 import math
+import os
 from typing import Optional, Tuple, Union
 
 import torch
@@ -303,8 +304,12 @@ def block_sparse_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, bl
     if tuple(block_idx.shape) != (B, Hq, lqb, lkb) or tuple(block_cnt.shape) != (B, Hq, lqb):
         raise ValueError("block lists have the wrong shape")
     if use_workspace is None:
-        use_workspace = ((lkb >= PAIR_MIN_K_BLOCKS and B * Hq * lqb >= PAIR_MIN_ITEMS) if causal
-                         else B * Hq * lqb >= ORDER_MIN_ITEMS)
+        forced = os.environ.get("XATTN_B200_ATTN_WORKSPACE")         # "0" / "1": overrides the rule (for measurements)
+        if forced in ("0", "1"):
+            use_workspace = forced == "1"
+        else:
+            use_workspace = ((lkb >= PAIR_MIN_K_BLOCKS and B * Hq * lqb >= PAIR_MIN_ITEMS) if causal
+                             else B * Hq * lqb >= ORDER_MIN_ITEMS)
     ws_bytes = lib.xattn_b200_block_sparse_attn_workspace_bytes(B, Hq, Hkv, Lq, Lk) if use_workspace else 0
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device) if ws_bytes else None
     _lib.check(lib.xattn_b200_block_sparse_attn_ws(
